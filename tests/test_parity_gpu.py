@@ -1,0 +1,264 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Tolerance (stated by the task for the fp32 output): max-abs error <= 2e-3 and
+per-sequence relative L2 error <= 1e-2.  Every case here is held to a tighter
+bound as well, so a regression shows before it reaches the limit.
+"""
+import ctypes
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import attention_oracle as orc
+from vte_b200.bridge.errors import CudaSafetyError
+from vte_b200.core.decode_executor import DecodeAttentionExecutor
+from vte_b200.workloads import CONFIGS, DecodeConfig, make_layer_inputs
+from tests.golden.make_golden import SMALL_CASES
+
+pytestmark = pytest.mark.gpu
+
+GOLD = Path(__file__).resolve().parent / "golden"
+MAX_ABS, REL_L2 = 2e-3, 1e-2
+TIGHT_ABS = 2e-4
+
+
+def metadata(cfg):
+    return {'attention.head_count': cfg.num_q_heads, 'attention.head_count_kv': cfg.num_kv_heads,
+            'attention.key_length': cfg.head_dim}
+
+
+def run_layer(rt, codegen, cfg, q, k, v, off, **kw):
+    ex = DecodeAttentionExecutor(rt, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 1, **kw)
+    try:
+        ex.upload_layer(0, q, k, v)
+        out = ex.execute_decode_batch(off)[0]
+        partials = ex.read_partials()
+        return out, partials, ex.dispatcher.max_chunks
+    finally:
+        ex.cleanup()
+
+
+def assert_parity(out, ref, tight=TIGHT_ABS):
+    assert np.all(np.isfinite(out))
+    max_abs, rel = orc.parity_metrics(out, ref)
+    assert max_abs <= MAX_ABS and rel <= REL_L2, (max_abs, rel)
+    assert max_abs <= tight, f"within tolerance but worse than expected: {max_abs}"
+
+
+def test_bridge_roundtrip_and_events(cuda_runtime):
+    rt = cuda_runtime
+    assert rt.get_gpu_architecture() == "sm_100a"
+    assert rt.get_num_cus() >= 100
+    x = np.arange(1 << 16, dtype=np.float32)
+    p = rt.safe_malloc(x.nbytes, "roundtrip output")
+    try:
+        rt.safe_memcpy_host_to_device(p, x, "roundtrip output")
+        y = np.zeros_like(x)
+        e0, e1 = rt.event_create(), rt.event_create()
+        rt.event_record(e0)
+        rt.safe_memcpy_device_to_host(y, p, "roundtrip output")
+        rt.event_record(e1)
+        assert rt.event_elapsed_ms(e0, e1) >= 0.0
+        rt.event_destroy(e0); rt.event_destroy(e1)
+        assert np.array_equal(x, y)
+        with pytest.raises(CudaSafetyError):
+            rt.safe_memcpy_host_to_device(ctypes.c_void_p(p.value + x.nbytes - 4), np.zeros(2, np.float32), "overflow")
+        with pytest.raises(CudaSafetyError):
+            rt.safe_memcpy_device_to_host(y, p, "weights")     # tag is not a result
+    finally:
+        rt.safe_free(p, "roundtrip output")
+    with pytest.raises(CudaSafetyError):
+        rt.safe_free(p, "double free")
+
+
+@pytest.mark.parametrize("compat", [True, False], ids=["compat", "fast"])
+@pytest.mark.parametrize("name", ["ragged_d64", "outlier_d256", "mha_d128", "group8_d128"])
+def test_small_cases_match_oracle_and_reference_vectors(cuda_runtime, codegen, name, compat):
+    cfg, lens = SMALL_CASES[name]
+    q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
+    ref = orc.decode_attention(q, k, v, off)
+    gold = np.load(GOLD / f"attn_{name}.npz")["out"]
+    for splits in (1, 3, 8):
+        out, (pm, pl, po), C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=splits, compat=compat,
+                                         min_chunk=0, strict_empty_splits=True)
+        assert_parity(out, ref)
+        assert_parity(out, gold)
+        # the partial buffers themselves follow the reference's split semantics
+        rm, rl, ro = orc.split_kv_partial(q, k, v, off, cfg.scale, C)
+        assert np.allclose(pm, rm, atol=1e-3, rtol=1e-5)
+        live = rm > -1e29
+        assert np.array_equal(pm[~live], rm[~live]) and np.all(pl[~live] == 0) and np.all(po[~live] == 0)
+        # (m, l, o) are only defined up to a common shift of m: compare l*exp(m) and o*exp(m) via the merged output
+        assert_parity(orc.split_kv_reduce(pm, pl, po), ref)
+
+
+@pytest.mark.parametrize("compat", [True, False], ids=["compat", "fast"])
+def test_config1_matches_reference_vector(cuda_runtime, codegen, compat):
+    cfg = CONFIGS["c1"]
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    gold = np.load(GOLD / "attn_c1.npz")["out"]
+    for splits in (None, 16):
+        out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=splits, compat=compat)
+        assert_parity(out, gold, tight=5e-5)
+
+
+def test_fixed_chunk_mode_reproduces_reference_chunking(cuda_runtime, codegen):
+    """-DSPLIT_KV_CHUNK_SIZE=32 build: split c covers [32c, 32c+32) as in the reference."""
+    cfg = CONFIGS["c1"]
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    ref = orc.decode_attention(q, k, v, off)
+    for compat in (True, False):
+        out, (pm, pl, po), C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, fixed_chunk_size=32, compat=compat,
+                                         strict_empty_splits=True)
+        assert C == 16
+        rm, rl, ro = orc.split_kv_partial(q, k, v, off, cfg.scale, C, chunk_size=32)
+        assert np.allclose(pm, rm, atol=1e-3)
+        assert np.allclose(pl, rl, rtol=2e-3, atol=1e-4)
+        assert np.allclose(po, ro, rtol=2e-3, atol=2e-3)
+        assert_parity(out, ref, tight=5e-5)
+
+
+@pytest.mark.parametrize("shape", [(12, 2, 128), (32, 8, 64), (8, 2, 256)], ids=["q12kv2d128", "q32kv8d64", "q8kv2d256"])
+def test_every_context_length_up_to_130(cuda_runtime, codegen, shape):
+    """Context lengths 1..130 cross every 16-position block and tile boundary and
+    leave most splits empty; one captured graph is replayed with new offsets."""
+    Hq, Hkv, D = shape
+    cfg = DecodeConfig("sweep", 21, 2, Hq, Hkv, D, 160, 160, 1)
+    q, k, v, _ = make_layer_inputs(cfg, 0)
+    for splits in (1, 4):
+        ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 1,
+                                     num_splits=splits, min_chunk=0)
+        try:
+            ex.upload_layer(0, q, k, v)
+            worst = 0.0
+            for n in range(1, 131):
+                off = np.array([n - 1, 130 - n], dtype=np.int32)
+                out = ex.execute_decode_batch(off)[0]
+                ref = orc.decode_attention(q, k, v, off)
+                max_abs, rel = orc.parity_metrics(out, ref)
+                worst = max(worst, max_abs)
+                assert max_abs <= TIGHT_ABS and rel <= 1e-3, (n, max_abs, rel)
+        finally:
+            ex.cleanup()
+
+
+def test_config2_layer_split_sweep(cuda_runtime, codegen):
+    """32k-context layer (RoPE'd Q) against the reference vector for split counts 8..256."""
+    cfg = CONFIGS["c2"]
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    gold = np.load(GOLD / "attn_c2_layer0.npz")["out"]
+    outs = {}
+    for splits in (8, 16, 32, 64, 128, 148, 256):
+        out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=splits)
+        assert_parity(out, gold, tight=2e-5)
+        outs[splits] = out
+    # split-count invariance: a size-independent property of the merge
+    for s, o in outs.items():
+        assert np.max(np.abs(o - outs[8])) < 1e-5, s
+    out_c, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=64, compat=True)
+    assert_parity(out_c, gold, tight=2e-5)
+
+
+def test_ragged_batch_matches_oracle(cuda_runtime, codegen):
+    """Config-3 shape at reduced size: 16 sequences, lengths 100..4096, work-queue path."""
+    cfg = DecodeConfig("c3_small", 3, 16, 32, 8, 64, 100, 4096, 1)
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    ref = orc.decode_attention(q, k, v, off)
+    out, _, C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off)
+    assert C == 16
+    assert_parity(out, ref, tight=5e-5)
+    out2, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=64, min_chunk=64)
+    assert_parity(out2, ref, tight=5e-5)
+
+
+def test_outlier_numerics_d256(cuda_runtime, codegen):
+    """Config-4 shape at reduced size: sigma 0.5 with 1% x20 outliers stresses max / LSE."""
+    cfg = DecodeConfig("c4_small", 4, 4, 8, 2, 256, 2048, 8192, 1, sigma_kv=0.5, outlier_frac=0.01, outlier_scale=20.0)
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    ref = orc.decode_attention(q, k, v, off)
+    out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off)
+    assert_parity(out, ref, tight=1e-3)
+    ref64 = orc.decode_attention(q, k, v, off, dtype=np.float64)
+    max_abs, rel = orc.parity_metrics(out, ref64)
+    assert max_abs <= MAX_ABS and rel <= REL_L2
+
+
+def test_direct_entry_point_equals_dispatcher_path(cuda_runtime, codegen):
+    """vteb_split_kv_decode (kernels linked into the library) and the cubin path
+    launched through the dispatcher give the same bits."""
+    rt = cuda_runtime
+    cfg, lens = SMALL_CASES["ragged_d64"]
+    q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
+    out_disp, _, C = run_layer(rt, codegen, cfg, q, k, v, off, num_splits=4, min_chunk=0)
+    B, Hq, Hkv, D = cfg.batch, cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+    bufs = {}
+    def dev(name, arr=None, nbytes=None):
+        n = arr.nbytes if arr is not None else nbytes
+        p = rt.safe_malloc(n, f"{name} output")
+        if arr is not None:
+            rt.safe_memcpy_host_to_device(p, arr, f"{name} output")
+        else:
+            rt.safe_memset(p, n, f"{name} output")
+        bufs[name] = p
+        return p
+    try:
+        dq, dk, dv, doff = dev("q", q), dev("k", k), dev("v", v), dev("off", off)
+        dout = dev("out", nbytes=B * Hq * D * 4)
+        pm, pl = dev("pm", nbytes=B * Hq * C * 4), dev("pl", nbytes=B * Hq * C * 4)
+        po, work = dev("po", nbytes=B * Hq * C * D * 4), dev("work", nbytes=16)
+        for flags in (0, 1):
+            rt.split_kv_decode(dq, dk, dv, doff, dout, True, pm, pl, po, work, B, Hq, Hkv, D, cfg.scale,
+                               cfg.kv_batch_stride, C, 0, flags)
+            rt.check_status(work)
+            out = np.zeros((B, Hq, D), dtype=np.float32)
+            rt.safe_memcpy_device_to_host(out, dout, "out output")
+            if flags == 0:
+                assert np.array_equal(out, out_disp)
+            else:
+                assert_parity(out, out_disp)
+        with pytest.raises(CudaSafetyError):
+            rt.split_kv_decode(dq, dk, dv, doff, dout, True, pm, pl, po, work, B, Hq, Hkv, 96, cfg.scale,
+                               cfg.kv_batch_stride, C, 0, 0)
+    finally:
+        for p in bufs.values():
+            rt.safe_free(p, "direct entry cleanup")
+
+
+def test_append_then_attend_in_one_graph(cuda_runtime, codegen):
+    """append -> partial -> combine recorded together: the new row must be visible
+    to the attention of the same step (with programmatic dependent launch on)."""
+    cfg = DecodeConfig("append", 22, 2, 12, 2, 128, 300, 300, 2)
+    ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 2, with_append=True,
+                                 num_splits=4, min_chunk=0)
+    try:
+        layers = [make_layer_inputs(cfg, l) for l in range(2)]
+        rng = np.random.default_rng(3)
+        for l, (q, k, v, _) in enumerate(layers):
+            ex.upload_layer(l, q, k, v)
+        for step, base in enumerate((40, 41, 255)):
+            off = np.array([base, base // 2], dtype=np.int32)
+            news = []
+            for l in range(2):
+                kn = rng.standard_normal((cfg.batch, 2, 128), dtype=np.float32).astype(np.float16)
+                vn = rng.standard_normal((cfg.batch, 2, 128), dtype=np.float32).astype(np.float16)
+                ex.upload_new_kv(l, kn, vn)
+                news.append((kn, vn))
+            out = ex.execute_decode_batch(off)
+            for l, (q, k, v, _) in enumerate(layers):
+                orc.kv_cache_append(news[l][0], news[l][1], k, v, off)
+                ref = orc.decode_attention(q, k, v, off)
+                assert_parity(out[l], ref, tight=5e-5)
+    finally:
+        ex.cleanup()
+
+
+def test_fp16_output_variant(cuda_runtime, codegen):
+    cfg, lens = SMALL_CASES["group8_d128"]
+    q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
+    ref = orc.decode_attention(q, k, v, off)
+    for compat in (True, False):
+        out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, output_f32=False, compat=compat, num_splits=4,
+                              min_chunk=0)
+        assert out.dtype == np.float16
+        assert np.max(np.abs(out.astype(np.float32) - ref)) <= 1e-3

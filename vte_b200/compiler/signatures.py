@@ -1,0 +1,39 @@
+"""Argument lists of every kernel the cubin exports, as ctypes types.
+
+The runtime checks the argument count of each launch against this table: the
+reference paid for a missing check of this kind with a GPU hang
+(docs/BUGS.md:35) and only validates counts when the caller passes
+`expected_args` (vte/bridge/hip_runtime.py:814-818).  The three reference-named
+kernels list exactly the arguments of
+kv_cache_append.hip.template:13-22,
+flash_attention_split_kv_partial.hip.template:31-45 and
+flash_attention_split_kv_reduce.hip.template:14-22.
+"""
+import ctypes
+
+P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+_REFERENCE_PARTIAL = [P, P, P, P, P, P, I, I, I, F, P, I, I]
+_FAST_PARTIAL = _REFERENCE_PARTIAL + [I, I, I, P, P, P]   # batch, min_chunk, flags, seq_order, ticket, status
+_REDUCE = [P, P, P, P, I, I, I]
+_FAST_COMBINE = _REDUCE + [I, P]                          # dsplit, ticket
+
+KERNEL_SIGNATURES = {
+    "kv_cache_append_kernel": [P, P, P, P, I, I, P, I],
+    "flash_attention_split_kv_partial_kernel": _REFERENCE_PARTIAL,
+    "flash_attention_split_kv_reduce_kernel": _REDUCE,
+    "flash_attention_split_kv_reduce_f32_kernel": _REDUCE,
+    "vteb_split_kv_partial_d64_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_d128_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_d256_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_combine_f16_kernel": _FAST_COMBINE,
+    "vteb_split_kv_combine_f32_kernel": _FAST_COMBINE,
+}
+
+# template name (what the reference passes to load_kernel_safe) -> source file
+TEMPLATE_SOURCES = {
+    "kv_cache_append": "decode_attention.cu",
+    "flash_attention_split_kv_partial": "decode_attention.cu",
+    "flash_attention_split_kv_reduce": "decode_attention.cu",
+    "decode_attention": "decode_attention.cu",
+}

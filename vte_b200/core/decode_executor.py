@@ -1,0 +1,244 @@
+"""Decode-step driver for the attention path: one captured CUDA graph per step.
+
+The attention-only counterpart of `HIPGraphExecutor` / `BatchedHIPGraphExecutor`
+(vte/core/hip_graph_executor.py:504-819, vte/core/batched_hip_graph_executor.py:
+231-292): it owns the per-layer buffers an executor would hand the dispatcher
+(`blk.{l}.q_proj.output`, `blk.{l}.k_proj.output`, `blk.{l}.v_proj.output`,
+`blk.{l}.attention.output`, `blk.{l}.kv_cache.k/.v`,
+`kv_batch_stride_elements`), records every layer's launches from
+`SplitKVAttentionDispatcher.build_launches` into one graph
+(hip_graph_executor.py:635-651), and replays it per token after rewriting the
+device array of per-sequence kv offsets from a staging buffer
+(hip_graph_executor.py:772-789; batched: batched_hip_graph_executor.py:276-285).
+Unlike the reference's batched executor it admits ragged context lengths.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import numpy as np
+
+from ..bridge.errors import CudaSafetyError
+from ..bridge.memory import MemoryRegion, SlabAllocator
+from ..config import ENV_NO_PDL, env_flag
+from .split_kv_attention import SplitKVAttentionDispatcher
+
+
+class DecodeAttentionExecutor:
+    def __init__(self, hip, codegen, metadata: dict, batch_size: int, context_length: int, n_layers: int, *,
+                 n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, output_f32: bool = True,
+                 use_graph: bool = True, programmatic: Optional[bool] = None, compat: bool = False,
+                 with_append: bool = False, fixed_chunk_size=None, min_chunk: Optional[int] = None,
+                 strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None):
+        self.hip = hip
+        self.metadata = dict(metadata)
+        self.B = int(batch_size)
+        self.S = int(context_length)
+        self.L = int(n_layers)
+        self.n_kv = int(n_kv_buffers or n_layers)   # distinct KV buffers; layers cycle through them
+        if not (1 <= self.n_kv <= self.L):
+            raise CudaSafetyError(f"n_kv_buffers {self.n_kv} outside 1..{self.L}")
+        self.Hq = int(metadata.get('attention.head_count', 12))
+        self.Hkv = int(metadata.get('attention.head_count_kv', 2))
+        self.D = int(metadata.get('attention.key_length', 128))
+        self.output_f32 = bool(output_f32)
+        self.use_graph = bool(use_graph)
+        self.programmatic = (not env_flag(ENV_NO_PDL)) if programmatic is None else bool(programmatic)
+        self.with_append = bool(with_append)
+        self.kv_batch_stride = self.S * self.Hkv * self.D
+        if self.kv_batch_stride >= 2 ** 31:
+            raise CudaSafetyError("one sequence's cache exceeds 2^31 elements: the kernel ABI's stride is an int")
+
+        out_elem = 4 if self.output_f32 else 2
+        self.kv_bytes = self.B * self.kv_batch_stride * 2           # one K (or V) cache of one layer
+        self.q_bytes = self.B * self.Hq * self.D * 2
+        self.kvnew_bytes = self.B * self.Hkv * self.D * 2
+        self.out_bytes = self.B * self.Hq * self.D * out_elem
+
+        self._owns_allocator = allocator is None
+        if allocator is None:
+            need = (2 * self.n_kv * (self.kv_bytes + 256) + self.L * (self.q_bytes + 2 * self.kvnew_bytes
+                    + self.out_bytes + 1024) + (64 << 20))
+            free_b, total_b = hip.get_real_mem_info()
+            allocator = SlabAllocator(hip, total_b, requested_pool_size=need)
+            allocator.initialize()
+        self.allocator = allocator
+        self.dispatcher = SplitKVAttentionDispatcher(
+            hip, codegen, self.metadata, allocator=allocator, context_length=self.S, batch_size=self.B,
+            num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
+            output_f32=self.output_f32, strict_empty_splits=strict_empty_splits)
+
+        A = allocator.allocate
+        self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
+        self.v_cache = [A(self.kv_bytes, f"kv_cache.v.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
+        # all layers' Q (and outputs) are contiguous so one copy moves a whole step's worth
+        self.q_all = A(self.L * self.q_bytes, "q_proj.output.all", MemoryRegion.ACTIVATIONS)
+        self.knew_all = A(self.L * self.kvnew_bytes, "k_proj.output.all", MemoryRegion.ACTIVATIONS)
+        self.vnew_all = A(self.L * self.kvnew_bytes, "v_proj.output.all", MemoryRegion.ACTIVATIONS)
+        self.out_all = A(self.L * self.out_bytes, "attention.output.all", MemoryRegion.ACTIVATIONS)
+        self.offsets = A(4 * self.B, "kv_offsets", MemoryRegion.ACTIVATIONS)
+
+        self.tensor_mapping = {'kv_batch_stride_elements': self.kv_batch_stride}
+        for l in range(self.L):
+            self.tensor_mapping[f'blk.{l}.q_proj.output'] = self.q_all.ptr + l * self.q_bytes
+            self.tensor_mapping[f'blk.{l}.k_proj.output'] = self.knew_all.ptr + l * self.kvnew_bytes
+            self.tensor_mapping[f'blk.{l}.v_proj.output'] = self.vnew_all.ptr + l * self.kvnew_bytes
+            self.tensor_mapping[f'blk.{l}.attention.output'] = self.out_all.ptr + l * self.out_bytes
+            self.tensor_mapping[f'blk.{l}.kv_cache.k'] = self.k_cache[l % self.n_kv]
+            self.tensor_mapping[f'blk.{l}.kv_cache.v'] = self.v_cache[l % self.n_kv]
+
+        # pinned staging: offsets, a step's Q, a step's outputs
+        self._stage_offsets = hip.host_alloc(4 * self.B)
+        self._stage_q = hip.host_alloc(self.L * self.q_bytes)
+        self._stage_out = hip.host_alloc(self.L * self.out_bytes)
+        self._graph_exec = None
+        self._launches = None
+        self.kernel_launches_per_step = 0
+
+    # ---- data movement helpers ----------------------------------------------------
+    def upload_layer(self, layer: int, q: np.ndarray, k_cache: Optional[np.ndarray] = None,
+                     v_cache: Optional[np.ndarray] = None):
+        """Host -> device of one layer's Q [B,Hq,D] and (optionally) its caches
+        [B,max_seq,Hkv,D], all fp16."""
+        self.hip.safe_memcpy_host_to_device(ctypes.c_void_p(self.q_all.ptr + layer * self.q_bytes),
+                                            np.ascontiguousarray(q, dtype=np.float16), "q upload")
+        if k_cache is not None:
+            self.upload_cache(layer % self.n_kv, k_cache, v_cache)
+
+    def upload_cache(self, buf: int, k_cache: np.ndarray, v_cache: np.ndarray):
+        for dst, src in ((self.k_cache[buf], k_cache), (self.v_cache[buf], v_cache)):
+            src = np.ascontiguousarray(src, dtype=np.float16)
+            if src.shape != (self.B, self.S, self.Hkv, self.D):
+                raise CudaSafetyError(f"cache shape {src.shape} != {(self.B, self.S, self.Hkv, self.D)}")
+            self.hip.safe_memcpy_host_to_device(ctypes.c_void_p(dst.ptr), src, "kv upload")
+
+    def upload_new_kv(self, layer: int, k_new: np.ndarray, v_new: np.ndarray):
+        self.hip.safe_memcpy_host_to_device(ctypes.c_void_p(self.knew_all.ptr + layer * self.kvnew_bytes),
+                                            np.ascontiguousarray(k_new, dtype=np.float16), "k_new upload")
+        self.hip.safe_memcpy_host_to_device(ctypes.c_void_p(self.vnew_all.ptr + layer * self.kvnew_bytes),
+                                            np.ascontiguousarray(v_new, dtype=np.float16), "v_new upload")
+
+    def fill_cache_on_device(self, buf: int, seed: int, sigma: float = 1.0, outlier_prob: float = 0.0,
+                             outlier_scale: float = 1.0):
+        """Synthetic N(0, sigma) cache contents generated on the device."""
+        n = self.B * self.kv_batch_stride
+        self.hip.fill_normal_f16(ctypes.c_void_p(self.k_cache[buf].ptr), n, 2 * seed + 1, sigma, outlier_prob, outlier_scale)
+        self.hip.fill_normal_f16(ctypes.c_void_p(self.v_cache[buf].ptr), n, 2 * seed + 2, sigma, outlier_prob, outlier_scale)
+
+    def download_cache_rows(self, buf: int, b: int, n_rows: int):
+        """(K, V) [n_rows, Hkv, D] fp16 of sequence b, for checking against the oracle."""
+        row = self.Hkv * self.D
+        k = np.empty((n_rows, self.Hkv, self.D), dtype=np.float16)
+        v = np.empty_like(k)
+        off = b * self.kv_batch_stride * 2
+        self.hip.safe_memcpy_device_to_host(k, ctypes.c_void_p(self.k_cache[buf].ptr + off), "kv rows for output check")
+        self.hip.safe_memcpy_device_to_host(v, ctypes.c_void_p(self.v_cache[buf].ptr + off), "kv rows for output check")
+        assert k.nbytes == n_rows * row * 2
+        return k, v
+
+    # ---- graph ----------------------------------------------------------------------
+    def _record_all(self):
+        n = 0
+        for l in range(self.L):
+            launches = self.dispatcher.build_launches(l, self.tensor_mapping, self.offsets.ptr, batch=self.B)
+            if not self.with_append:
+                launches = launches[1:]
+            for fn, args, grid, block, smem in launches:
+                self.hip.launch_kernel_recorded(fn, args, grid, block, smem)
+                n += 1
+        return n
+
+    def build_decode_graph(self):
+        """Capture all layers' launches once (hip_graph_executor.py:504-725)."""
+        if self._graph_exec is not None:
+            return
+        self.hip.programmatic_launch = self.programmatic
+        try:
+            if not self.use_graph:
+                self.kernel_launches_per_step = (3 if self.with_append else 2) * self.L
+                return
+            self.hip.stream_begin_capture()
+            try:
+                self.kernel_launches_per_step = self._record_all()
+            finally:
+                graph = self.hip.stream_end_capture()
+            self._graph_exec = self.hip.graph_instantiate(graph)
+            self.hip.graph_destroy(graph)
+        finally:
+            self.hip.programmatic_launch = False
+
+    def _update_staging_buffers(self, kv_offsets: np.ndarray):
+        off = np.ascontiguousarray(kv_offsets, dtype=np.int32)
+        if off.shape != (self.B,):
+            raise CudaSafetyError(f"kv_offsets shape {off.shape} != ({self.B},)")
+        if off.min() < 0 or off.max() >= self.S:
+            raise CudaSafetyError(f"kv offset outside 0..{self.S - 1}")
+        ctypes.memmove(self._stage_offsets.value, off.ctypes.data, off.nbytes)
+        self.hip.memcpy_h2d_async(ctypes.c_void_p(self.offsets.ptr), self._stage_offsets, off.nbytes, "kv_offsets")
+
+    def launch_step(self):
+        """Enqueue one decode step (no host synchronisation)."""
+        if self._graph_exec is not None:
+            self.hip.graph_launch(self._graph_exec)
+        else:
+            self.hip.programmatic_launch = self.programmatic
+            try:
+                self._record_all()
+            finally:
+                self.hip.programmatic_launch = False
+
+    def execute_decode_batch(self, kv_offsets: np.ndarray, q_host: Optional[np.ndarray] = None,
+                             read_output: bool = True) -> Optional[np.ndarray]:
+        """One decode step end to end: stage offsets (and, when given, every layer's
+        Q [L,B,Hq,D] fp16) host -> device, replay the graph, read every layer's
+        output back.  Returns [L,B,Hq,D] (fp32 or fp16)."""
+        self.build_decode_graph()
+        self._update_staging_buffers(kv_offsets)
+        if q_host is not None:
+            qh = np.ascontiguousarray(q_host, dtype=np.float16)
+            if qh.nbytes != self.L * self.q_bytes:
+                raise CudaSafetyError("q_host must be [L, B, Hq, D] fp16")
+            ctypes.memmove(self._stage_q.value, qh.ctypes.data, qh.nbytes)
+            self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, qh.nbytes, "q staging")
+        self.launch_step()
+        if not read_output:
+            return None
+        nbytes = self.L * self.out_bytes
+        self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), nbytes, "attention output")
+        self.hip.stream_synchronize()
+        self.dispatcher_check()
+        dt = np.float32 if self.output_f32 else np.float16
+        flat = np.frombuffer((ctypes.c_char * nbytes).from_address(self._stage_out.value), dtype=dt)
+        return flat.reshape(self.L, self.B, self.Hq, self.D).copy()
+
+    execute_decode = execute_decode_batch
+
+    def dispatcher_check(self):
+        """Raise if a split kernel reported a timed-out wait."""
+        if self.dispatcher.work_ptr and hasattr(self.hip, "check_status"):
+            self.hip.check_status(ctypes.c_void_p(self.dispatcher.work_ptr))
+
+    def read_partials(self):
+        """(partial_m, partial_l [B,Hq,C], partial_o [B,Hq,C,D]) of the last layer run."""
+        pm, pl, po = self.dispatcher.partial_buffers
+        C = self.dispatcher.max_chunks
+        m = np.empty((self.B, self.Hq, C), dtype=np.float32)
+        l = np.empty_like(m)
+        o = np.empty((self.B, self.Hq, C, self.D), dtype=np.float32)
+        self.hip.safe_memcpy_device_to_host(m, ctypes.c_void_p(pm.ptr), "partial output m")
+        self.hip.safe_memcpy_device_to_host(l, ctypes.c_void_p(pl.ptr), "partial output l")
+        self.hip.safe_memcpy_device_to_host(o, ctypes.c_void_p(po.ptr), "partial output o")
+        return m, l, o
+
+    def cleanup(self):
+        if self._graph_exec is not None:
+            self.hip.graph_exec_destroy(self._graph_exec)
+            self._graph_exec = None
+        for p in (self._stage_offsets, self._stage_q, self._stage_out):
+            if p is not None and p.value:
+                self.hip.host_free(p)
+        self._stage_offsets = self._stage_q = self._stage_out = None
+        if self._owns_allocator:
+            self.allocator.cleanup()

@@ -1,0 +1,249 @@
+"""Split-KV (flash-decoding) attention dispatcher for decode (one query token).
+
+Drop-in for `SplitKVAttentionDispatcher` of vte/core/split_kv_attention.py:52-229:
+same constructor arguments, same `.enabled` switch (`VTE_DISABLE_ATTN_SPLITKV`),
+same `build_launches(layer_idx, tensor_mapping, kv_offset_ptr, batch, q_name,
+k_name, v_name)` returning three `(function, args, grid, block, shared_mem)`
+tuples (append, partial, reduce) that an executor records with
+`launch_kernel_recorded`, same scratch policy (one set of partial buffers shared
+by all layers, :114-128), same tensor-name resolution (:72-98, :166-176).
+
+What differs is what the tuples launch.  By default the partial launch is the
+persistent sm_100a kernel (`vteb_split_kv_partial_d*_kernel`, grid = one CTA per
+SM) and the reduce launch is `vteb_split_kv_combine_*`; `compat=True` (or
+`VTE_B200_COMPAT_KERNELS=1`) emits the reference-named kernels with the
+reference's own grids instead.  `max_chunks` is a split COUNT unless
+`fixed_chunk_size` is given, in which case the reference's arithmetic
+(`max_chunks = ceil(context_length / chunk_size)`, :61-62) is used and the
+kernels are compiled with that chunk length.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+from ..bridge.errors import CudaSafetyError
+from ..bridge.memory import MemoryRegion
+from ..config import ENV_COMPAT_KERNELS, ENV_DISABLE_SPLITKV
+
+SPLIT_KV_CHUNK_SIZE = 32          # the reference's historical chunk (RX 7600, 32 CUs)
+MAX_SPLITS = 256
+TARGET_CHUNK_POSITIONS = 256      # chunk length aimed at when many sequences share the GPU
+FLAG_WRITE_EMPTY_O = 1
+
+
+def _chunk_size_for_cus(num_cus: int) -> int:
+    """The reference's rule (vte/core/split_kv_attention.py:40-49): 1024 / CUs,
+    rounded, kept within [8, 64]; 32 when the count is unknown."""
+    if num_cus <= 0:
+        return SPLIT_KV_CHUNK_SIZE
+    return max(8, min(64, round(1024 / num_cus)))
+
+
+def choose_split_count(num_sms: int, batch: int, n_hgroups: int, context_length: int) -> int:
+    """Split count when the caller does not fix one.
+
+    One sequence: as many splits as SMs, so the persistent grid is exactly one
+    wave of equal work items.  Several sequences: chunks of about 256 positions
+    (capped at 256 splits for the longest context), so that ragged lengths
+    balance through the work queue while the fp32 partials stay a few percent
+    of the K/V bytes.
+    """
+    if batch * n_hgroups <= 1:
+        return max(1, min(MAX_SPLITS, num_sms))
+    if batch == 1:
+        return max(1, min(MAX_SPLITS, num_sms // n_hgroups))
+    return max(1, min(MAX_SPLITS, math.ceil(context_length / TARGET_CHUNK_POSITIONS)))
+
+
+class SplitKVAttentionDispatcher:
+    def __init__(self, hip, codegen, metadata: dict, allocator=None, context_length: int = 4096,
+                 batch_size: int = 1, *, num_splits: int | None = None, fixed_chunk_size=None,
+                 compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
+                 strict_empty_splits: bool = False):
+        self.hip = hip
+        self.codegen = codegen
+        self.metadata = metadata or {}
+        self.allocator = allocator
+        self.batch_size = int(batch_size)
+        self.context_length = int(context_length)
+        self.output_f32 = bool(output_f32)
+        self.strict_empty_splits = bool(strict_empty_splits)
+        self.compat = bool(os.environ.get(ENV_COMPAT_KERNELS)) if compat is None else bool(compat)
+
+        self.num_q_heads = int(self.metadata.get('attention.head_count', 12))
+        self.num_kv_heads = int(self.metadata.get('attention.head_count_kv', 2))
+        self.head_dim = int(self.metadata.get('attention.key_length', 128))
+        num_cus = hip.get_num_cus() if hip is not None and hasattr(hip, 'get_num_cus') else 32
+        self.num_sms = num_cus
+
+        self._plan = None
+        if hip is not None and hasattr(hip, 'split_kv_plan'):
+            self._plan = hip.split_kv_plan(self.num_q_heads, self.num_kv_heads, self.head_dim)
+        if not self.compat and (self._plan is None or not self._plan.ok):
+            # geometry outside the fast kernel (group > 8, unusual head_dim): reference-geometry kernels
+            self.compat = True
+
+        if fixed_chunk_size is not None:
+            self.chunk_size = _chunk_size_for_cus(num_cus) if fixed_chunk_size == "auto" else int(fixed_chunk_size)
+            if self.chunk_size <= 0:
+                raise CudaSafetyError(f"fixed_chunk_size must be positive, got {fixed_chunk_size}")
+            self.max_chunks = max(1, math.ceil(self.context_length / self.chunk_size))
+            self.fixed_chunk = True
+        else:
+            self.fixed_chunk = False
+            n_hg = self._plan.n_hgroups if (self._plan is not None and self._plan.ok) else self.num_kv_heads
+            self.max_chunks = int(num_splits) if num_splits else choose_split_count(
+                num_cus, self.batch_size, n_hg, self.context_length)
+            if not (1 <= self.max_chunks <= 65535):
+                raise CudaSafetyError(f"split count {self.max_chunks} outside 1..65535")
+            self.chunk_size = 0
+        if min_chunk is None:
+            min_chunk = TARGET_CHUNK_POSITIONS if (self.batch_size > 1 and not self.fixed_chunk) else 0
+        self.min_chunk = int(min_chunk)
+
+        self._kernel_cache = {}
+        self._partial_m = self._partial_l = self._partial_o = self._work = None
+        self.enabled = not bool(os.environ.get(ENV_DISABLE_SPLITKV)) and allocator is not None
+
+    # -- tensor-name resolution -------------------------------------------------
+    @staticmethod
+    def _resolve_ptr(tensor_mapping: dict, name: str) -> int:
+        p = tensor_mapping.get(name)
+        if p is None:
+            return 0
+        return int(p.ptr) if hasattr(p, 'ptr') else int(p)
+
+    def _resolve_kv_cache_ptrs(self, layer_idx: int, tensor_mapping: dict):
+        """`blk.{l}.kv_cache.k/.v`, then `kv_cache.layer_{l}.k/.v`, then the pooled
+        layout (per layer: K block, then V block, each
+        batch * Hkv * D * 2 * context_length bytes; vte/compiler/qwen_mapper.py:321-351)."""
+        def get(*names):
+            for n in names:
+                p = tensor_mapping.get(n)
+                if p is not None:
+                    return int(p.ptr) if hasattr(p, 'ptr') else int(p)
+            return None
+        k_ptr = get(f'blk.{layer_idx}.kv_cache.k', f'kv_cache.layer_{layer_idx}.k')
+        v_ptr = get(f'blk.{layer_idx}.kv_cache.v', f'kv_cache.layer_{layer_idx}.v')
+        if k_ptr is None or v_ptr is None:
+            pool = get('KV Cache Pool')
+            if pool is not None:
+                half = self.batch_size * self.num_kv_heads * self.head_dim * 2 * self.context_length
+                k_ptr = pool + layer_idx * 2 * half
+                v_ptr = k_ptr + half
+        return int(k_ptr or 0), int(v_ptr or 0)
+
+    # -- kernels and scratch ------------------------------------------------------
+    def _get_kernels(self):
+        if 'append' not in self._kernel_cache:
+            arch = self.hip.get_gpu_architecture()
+            params = {'split_kv_chunk_size': self.chunk_size} if self.fixed_chunk else {}
+            load = lambda template, symbol: self.codegen.load_kernel_safe(self.hip, template, arch, symbol, **params)[1]
+            self._kernel_cache['append'] = load('kv_cache_append', 'kv_cache_append_kernel')
+            if self.compat:
+                self._kernel_cache['partial'] = load('flash_attention_split_kv_partial',
+                                                     'flash_attention_split_kv_partial_kernel')
+                self._kernel_cache['reduce'] = load(
+                    'flash_attention_split_kv_reduce',
+                    'flash_attention_split_kv_reduce_f32_kernel' if self.output_f32
+                    else 'flash_attention_split_kv_reduce_kernel')
+            else:
+                self._kernel_cache['partial'] = load('decode_attention', f'vteb_split_kv_partial_d{self.head_dim}_kernel')
+                self._kernel_cache['reduce'] = load(
+                    'decode_attention',
+                    'vteb_split_kv_combine_f32_kernel' if self.output_f32 else 'vteb_split_kv_combine_f16_kernel')
+
+            # One scratch set shared by every layer: layers run strictly one after
+            # another inside a decode step, so rewriting the same buffers is safe.
+            stats_size = self.batch_size * self.num_q_heads * self.max_chunks * 4
+            o_size = stats_size * self.head_dim
+            self._partial_m = self.allocator.allocate(stats_size, "attn_splitkv_m", MemoryRegion.SCRATCH)
+            self._partial_l = self.allocator.allocate(stats_size, "attn_splitkv_l", MemoryRegion.SCRATCH)
+            self._partial_o = self.allocator.allocate(o_size, "attn_splitkv_o", MemoryRegion.SCRATCH)
+            # work[0]: work-queue ticket (zero between launches), work[1]: status word
+            self._work = self.allocator.allocate(16, "attn_splitkv_work", MemoryRegion.SCRATCH)
+            if hasattr(self.hip, 'safe_memset'):
+                self.hip.safe_memset(ctypes.c_void_p(self._work.ptr), 16, "attn_splitkv_work")
+        return self._kernel_cache['append'], self._kernel_cache['partial'], self._kernel_cache['reduce']
+
+    @property
+    def work_ptr(self) -> int:
+        return self._work.ptr if self._work is not None else 0
+
+    @property
+    def partial_buffers(self):
+        return self._partial_m, self._partial_l, self._partial_o
+
+    # -- launches -----------------------------------------------------------------
+    def _validate(self, batch, q_ptr, k_cache_ptr, v_cache_ptr, output_ptr, kv_offset_ptr, kv_batch_stride):
+        if batch <= 0 or batch > self.batch_size:
+            raise CudaSafetyError(f"batch {batch} outside 1..{self.batch_size} (scratch is sized for batch_size)")
+        for name, p in (("q", q_ptr), ("k_cache", k_cache_ptr), ("v_cache", v_cache_ptr),
+                        ("attention output", output_ptr), ("kv offsets", kv_offset_ptr)):
+            if not p:
+                raise CudaSafetyError(f"{name} pointer could not be resolved (null)")
+        for name, p in (("q", q_ptr), ("k_cache", k_cache_ptr), ("v_cache", v_cache_ptr)):
+            if p % 16:
+                raise CudaSafetyError(f"{name} pointer 0x{p:X} is not 16-byte aligned")
+        if self.head_dim not in (64, 128, 256):
+            raise CudaSafetyError(f"head_dim {self.head_dim} not supported (64, 128, 256)")
+        if self.num_q_heads % self.num_kv_heads:
+            raise CudaSafetyError(f"{self.num_q_heads} query heads are not a multiple of {self.num_kv_heads} KV heads")
+        if kv_batch_stride < 0 or kv_batch_stride >= 2 ** 31:
+            raise CudaSafetyError(f"kv_batch_stride_elements {kv_batch_stride} does not fit the kernel's int argument")
+        if kv_batch_stride % 8:
+            raise CudaSafetyError(f"kv_batch_stride_elements {kv_batch_stride} must be a multiple of 8")
+        if batch > 1 and kv_batch_stride == 0:
+            raise CudaSafetyError("kv_batch_stride_elements is 0 with batch > 1: sequences would alias")
+
+    def build_launches(self, layer_idx: int, tensor_mapping: dict, kv_offset_ptr: int, batch: int = 1,
+                       q_name: str = None, k_name: str = None, v_name: str = None):
+        """[(append_fn, args, grid, block, smem), (partial_fn, ...), (reduce_fn, ...)]
+        for one layer.  Names default to the reference's convention
+        (`blk.{l}.q_proj.output` etc.); pass the graph node's real input names
+        when RoPE or a per-head norm writes elsewhere."""
+        append_fn, partial_fn, reduce_fn = self._get_kernels()
+        Hq, Hkv, D, C = self.num_q_heads, self.num_kv_heads, self.head_dim, self.max_chunks
+        attention_scale = self.metadata.get('attention_scale')
+        scale = float(attention_scale) if attention_scale else 1.0 / math.sqrt(D)
+
+        q_ptr = self._resolve_ptr(tensor_mapping, q_name or f'blk.{layer_idx}.q_proj.output')
+        k_proj_ptr = self._resolve_ptr(tensor_mapping, k_name or f'blk.{layer_idx}.k_proj.output')
+        v_proj_ptr = self._resolve_ptr(tensor_mapping, v_name or f'blk.{layer_idx}.v_proj.output')
+        output_ptr = self._resolve_ptr(tensor_mapping, f'blk.{layer_idx}.attention.output')
+        k_cache_ptr, v_cache_ptr = self._resolve_kv_cache_ptrs(layer_idx, tensor_mapping)
+        kv_batch_stride = int(tensor_mapping.get('kv_batch_stride_elements', 0))
+        kv_offset_ptr = int(kv_offset_ptr.value or 0) if isinstance(kv_offset_ptr, ctypes.c_void_p) else int(kv_offset_ptr or 0)
+        self._validate(batch, q_ptr, k_cache_ptr, v_cache_ptr, output_ptr, kv_offset_ptr, kv_batch_stride)
+
+        vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        append_args = [vp(k_proj_ptr), vp(v_proj_ptr), vp(k_cache_ptr), vp(v_cache_ptr),
+                       ci(Hkv), ci(D), vp(kv_offset_ptr), ci(kv_batch_stride)]
+        append = (append_fn, append_args, (batch, Hkv, 1), (D, 1, 1), 0)
+
+        reference_partial_args = [
+            vp(q_ptr), vp(k_cache_ptr), vp(v_cache_ptr),
+            vp(self._partial_m.ptr), vp(self._partial_l.ptr), vp(self._partial_o.ptr),
+            ci(Hq), ci(Hkv), ci(D), cf(scale), vp(kv_offset_ptr), ci(kv_batch_stride), ci(C)]
+        reduce_args = [vp(self._partial_m.ptr), vp(self._partial_l.ptr), vp(self._partial_o.ptr),
+                       vp(output_ptr), ci(Hq), ci(D), ci(C)]
+
+        if self.compat:
+            partial = (partial_fn, reference_partial_args, (batch, Hq, C), (D, 1, 1), 2 * D * 4)
+            reduce = (reduce_fn, reduce_args, (batch, Hq, 1), (D, 1, 1), C * 4)
+            return [append, partial, reduce]
+
+        plan = self._plan
+        items = batch * plan.n_hgroups * C
+        n_ctas = max(1, min(items, self.num_sms))
+        flags = FLAG_WRITE_EMPTY_O if self.strict_empty_splits else 0
+        partial_args = reference_partial_args + [
+            ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4)]
+        partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
+        dsplit = plan.combine_dsplit
+        combine_args = reduce_args + [ci(dsplit), vp(self._work.ptr)]
+        combine_smem = C * 4 + 8 * (D // dsplit) * 4
+        combine = (reduce_fn, combine_args, (batch * Hq * dsplit, 1, 1), (256, 1, 1), combine_smem)
+        return [append, partial, combine]

@@ -1,0 +1,226 @@
+// Shared device helpers for the sm_100a decode-attention kernels: mbarrier and
+// bulk-copy wrappers with bounded waits, ldmatrix / mma.sync wrappers, and the
+// shared-memory plan that host and device code both derive from the head
+// geometry.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace vteb {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kProducerWarp = kConsumerWarps;            // warp index of the loader warp
+constexpr int kFastThreads = (kConsumerWarps + 1) * 32;  // 288
+constexpr int kMaxStages = 8;
+constexpr int kBlockPos = 16;                            // positions per mma step
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kNeutralM = -1e30f;                      // reference's "empty split" maximum
+constexpr int kSmemBudget = 227 * 1024;                  // opt-in dynamic shared memory per CTA
+
+// Status word written by a kernel that gave up on a wait.  The host reads it
+// after synchronising; zero means every wait completed.
+constexpr int kStatusOk = 0;
+constexpr int kStatusFullTimeout = 1;    // consumer never saw a tile arrive
+constexpr int kStatusEmptyTimeout = 2;   // loader never got a stage back
+constexpr int kStatusMergeTimeout = 3;   // cross-warp merge barrier never completed
+
+// Tile flags carried in the per-stage header.
+constexpr int kTileFirst = 1;   // first tile of a work item: reset state, fetch Q
+constexpr int kTileLast = 2;    // last tile of a work item: merge warps, store partials
+constexpr int kTileEmpty = 4;   // item has no positions: store the neutral state
+constexpr int kTileStop = 8;    // no more work for this CTA
+
+struct TileHeader {
+    int b;        // sequence index
+    int hgroup;   // KV-head group index
+    int c;        // split index
+    int blk0;     // index, within the item, of the first 16-position block of this tile
+    int nvalid;   // positions of this tile that belong to the item
+    int flags;
+    int pos0;     // absolute position of the tile's first row
+    int pad;
+};
+
+// Everything the launch geometry depends on.  Computed identically on the host
+// (to size the launch) and on the device (to carve shared memory).
+struct FastPlan {
+    int hg;            // KV heads staged together per work item
+    int n_hgroups;     // ceil(num_kv_heads / hg)
+    int wph;           // consumer warps per KV head
+    int active_warps;  // wph * hg
+    int tile;          // positions per stage
+    int row_bytes;     // bytes of one position's K (or V) row for the head group
+    int row_pitch;     // row_bytes + 16: keeps ldmatrix row addresses on distinct banks
+    int stage_bytes;   // K tile + V tile
+    int merge_bytes;   // per-warp (m, l, o) exchange area
+    int q_bytes;       // per-thread Q fragment store (keeps the fragments out of registers)
+    int nstages;
+    int smem_bytes;    // total dynamic shared memory
+    int ok;            // 0 when the geometry is outside what the fast kernel covers
+};
+
+constexpr int kCtrlBytes = 1024;   // barriers, abort word, tile headers
+constexpr int kMergePad = 8;       // floats after o[D] in an exchange row: 4 unused, m, l, 2 unused
+
+__host__ __device__ inline int vteb_round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+__host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim) {
+    FastPlan p;
+    p.ok = 0;
+    p.hg = p.n_hgroups = p.wph = p.active_warps = p.tile = p.row_bytes = p.row_pitch = 0;
+    p.stage_bytes = p.merge_bytes = p.q_bytes = p.nstages = p.smem_bytes = 0;
+    if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0) return p;
+    int group = num_q_heads / num_kv_heads;
+    if (group > 8) return p;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return p;
+    // Largest divisor of num_kv_heads with hg * head_dim <= 512 halves and hg <= 8.
+    int cap = 512 / head_dim;
+    if (cap > kConsumerWarps) cap = kConsumerWarps;
+    int hg = 1;
+    for (int d = 1; d <= cap; ++d) if (num_kv_heads % d == 0) hg = d;
+    p.hg = hg;
+    p.n_hgroups = num_kv_heads / hg;
+    p.wph = kConsumerWarps / hg;
+    p.active_warps = p.wph * hg;
+    p.row_bytes = hg * head_dim * 2;
+    p.row_pitch = p.row_bytes + 16;
+    int tile = (16384 / p.row_bytes) / kBlockPos * kBlockPos;
+    if (tile < kBlockPos) tile = kBlockPos;
+    if (tile > 64) tile = 64;
+    p.tile = tile;
+    p.stage_bytes = vteb_round_up(2 * tile * p.row_pitch, 128);
+    p.merge_bytes = vteb_round_up(p.active_warps * group * (head_dim + kMergePad) * 4, 128);
+    p.q_bytes = kConsumerWarps * (head_dim / 8) * 32 * 4;
+    int left = kSmemBudget - kCtrlBytes - p.merge_bytes - p.q_bytes;
+    int n = left / p.stage_bytes;
+    if (n > kMaxStages) n = kMaxStages;
+    if (n < 2) return p;
+    p.nstages = n;
+    p.smem_bytes = kCtrlBytes + p.merge_bytes + p.q_bytes + n * p.stage_bytes;
+    p.ok = 1;
+    return p;
+}
+
+// Positions covered by one split of a sequence with `total` cached positions.
+// `fixed_chunk > 0` is the reference's compile-time chunk length; otherwise the
+// chunk is ceil(total / max_chunks) rounded up to 16 and not below `min_chunk`.
+__host__ __device__ inline int split_chunk_len(int total, int max_chunks, int fixed_chunk, int min_chunk) {
+    if (fixed_chunk > 0) return fixed_chunk;
+    int chunk = (total + max_chunks - 1) / max_chunks;
+    chunk = vteb_round_up(chunk < 1 ? 1 : chunk, kBlockPos);
+    if (chunk < min_chunk) chunk = vteb_round_up(min_chunk, kBlockPos);
+    return chunk;
+}
+
+#if defined(__CUDACC__)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        "  .reg .pred p;\n"
+        "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "  selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for a barrier phase for at most `limit_ns` of wall time, also giving
+// up as soon as another warp of the CTA has raised `*abort_word` (pass nullptr
+// to ignore it).  Returns false when it gave up; the caller then records a
+// status code and leaves.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word,
+                                                  uint64_t limit_ns = 2000000000ull) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t spin = 1; spin < (1u << 30); ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 0xFF) == 0) {
+            if (abort_word != nullptr && *abort_word != 0) return false;
+            if (global_timer_ns() - t0 > limit_ns) return false;
+        }
+    }
+    return false;
+}
+
+// One row of K or V: global -> this CTA's shared memory, completion counted on
+// an mbarrier.  Source, destination and size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load_row(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+// D(16x8, f32) += A(16x16, f16) * B(16x8, f16) where rows 8..15 of A are zero:
+// only the two accumulators of row (lane / 4) are kept.
+__device__ __forceinline__ void mma_rows0to7(float& d0, float& d1, uint32_t a_lo, uint32_t a_hi, uint32_t b0, uint32_t b1) {
+    float u0, u1;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%11};"
+        : "+f"(d0), "+f"(d1), "=f"(u0), "=f"(u1)
+        : "r"(a_lo), "r"(0u), "r"(a_hi), "r"(0u), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float x, float y) {
+    __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace vteb
