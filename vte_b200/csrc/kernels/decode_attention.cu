@@ -24,6 +24,17 @@
 
 using namespace vteb;
 
+// Optional timeline trace for kernel development (-DVTEB_TRACE): CTA 0 records
+// clock64() at a few points per tile into a global buffer.  Compiled out otherwise.
+#ifdef VTEB_TRACE
+__device__ long long vteb_trace_buf[9 * 64 * 4];
+#define VTEB_TRACE_EVENT(warp_, tile_, slot_) \
+    do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile_) < 64) \
+        vteb_trace_buf[((warp_) * 64 + (tile_)) * 4 + (slot_)] = clock64(); } while (0)
+#else
+#define VTEB_TRACE_EVENT(warp_, tile_, slot_) do {} while (0)
+#endif
+
 #ifndef SPLIT_KV_CHUNK_SIZE
 #define SPLIT_KV_CHUNK_SIZE 0   // > 0 reproduces the reference's fixed chunk length
 #endif
@@ -354,393 +365,4 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f32_kern
     fast_combine_body<float>(partial_m, partial_l, partial_o, output, num_q_heads, head_dim, max_chunks, dsplit, ticket);
 }
 
-// ---------------------------------------------------------------------------
-// Fast split kernel.
-//
-// grid (n_ctas, 1, 1) persistent, block 288 = eight consumer warps + one loader
-// warp, dynamic shared memory from make_fast_plan().  A work item is one split
-// of one sequence for one group of `hg` KV heads; item t maps to
-// (sequence rank t / (n_hgroups * C), head group, split).  CTA i starts with
-// item i and draws the following ones from `*ticket` (gridDim.x + atomicAdd).
-//
-// Loader warp: for every tile of `tile` positions, waits for a free stage,
-// writes the tile header, announces the byte count on the stage's "full"
-// mbarrier and issues one bulk asynchronous copy per position row of K and of
-// V (row_bytes contiguous bytes covering the group's heads) into rows padded by
-// 16 bytes.  Rows past the end of the item are filled from the item's last row
-// so that every row a consumer touches holds finite numbers.
-//
-// Consumer warp w: KV head (w % hg) of the group, every wph-th 16-position
-// block.  Per block: S = Q K^T with mma.sync m16n8k16 (Q rows are the query
-// heads of the KV head, K fragments via ldmatrix), online softmax in the log2
-// domain on the accumulator fragment, P split into an fp16 high and low part,
-// O += P V with V fragments via ldmatrix.trans.  At the end of an item the
-// warps of a KV head exchange (m, l, o) through shared memory and the merged
-// state is stored to partial_m / partial_l / partial_o.
-//
-// Every wait is bounded; a wait that gives up stores a code in `*status`,
-// raises the CTA's abort word, and the CTA drains its outstanding copies
-// (again bounded) and returns.
-// ---------------------------------------------------------------------------
-struct FastArgs {
-    const __half* q; const __half* k_cache; const __half* v_cache;
-    float* partial_m; float* partial_l; float* partial_o;
-    int num_q_heads, num_kv_heads; float scale;
-    const int* kv_offsets; long long kv_batch_stride; int max_chunks;
-    int batch, min_chunk, flags; const int* seq_order; int* ticket; int* status;
-};
-
-constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
-
-template <int D>
-__device__ __forceinline__ void fast_partial_body(const FastArgs& a)
-{
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const FastPlan plan = make_fast_plan(a.num_q_heads, a.num_kv_heads, D);
-    const int group = a.num_q_heads / a.num_kv_heads;
-
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);          // full[8], empty[8], merge[2]
-    volatile int* abort_word = reinterpret_cast<volatile int*>(smem_raw + 256);
-    TileHeader* headers = reinterpret_cast<TileHeader*>(smem_raw + 512);   // 8 * 32 B
-    float* merge = reinterpret_cast<float*>(smem_raw + kCtrlBytes);
-    uint32_t* q_store = reinterpret_cast<uint32_t*>(smem_raw + kCtrlBytes + plan.merge_bytes);
-    unsigned char* stages = smem_raw + kCtrlBytes + plan.merge_bytes + plan.q_bytes;
-
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
-    const uint32_t merge_bar0 = smem_u32(bars + 2 * kMaxStages);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, plan.active_warps);
-        }
-        mbar_init(merge_bar0, plan.active_warps);
-        mbar_init(merge_bar0 + 8, plan.active_warps);
-        *abort_word = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    grid_launch_dependents();
-
-    const int items_per_seq = plan.n_hgroups * a.max_chunks;
-    const int total_items = a.batch * items_per_seq;
-    const int nstages = plan.nstages;
-
-    if (warp == kProducerWarp) {
-        // ------------------------------ loader ------------------------------
-        int stage = 0;
-        uint32_t empty_parity = 0;      // bit s: parity to wait for on empty[s]
-        int filled = 0;                 // stages handed out so far
-        bool dep_done = false;
-        bool alive = true;
-        int item = blockIdx.x;
-        auto acquire = [&]() -> bool {
-            if (filled >= nstages) {
-                if (!mbar_wait_bounded(empty0 + 8 * stage, (empty_parity >> stage) & 1u, abort_word)) {
-                    if (lane == 0) { if (*abort_word == 0) atomicCAS(a.status, 0, kStatusEmptyTimeout); *abort_word = 1; }
-                    return false;
-                }
-                empty_parity ^= (1u << stage);
-            }
-            return true;
-        };
-        auto publish_header_only = [&](int b, int hgi, int c, int flags) {
-            if (lane == 0) {
-                TileHeader h; h.b = b; h.hgroup = hgi; h.c = c; h.blk0 = 0; h.nvalid = 0; h.flags = flags; h.pos0 = 0; h.pad = 0;
-                headers[stage] = h;
-                mbar_arrive(full0 + 8 * stage);
-            }
-            __syncwarp();
-            ++filled;
-            stage = (stage + 1 == nstages) ? 0 : stage + 1;
-        };
-        while (alive && item < total_items) {
-            const int rank = item / items_per_seq;
-            const int rem = item - rank * items_per_seq;
-            const int hgi = rem / a.max_chunks, c = rem - hgi * a.max_chunks;
-            const int b = a.seq_order ? a.seq_order[rank] : rank;
-            const int total = a.kv_offsets[b] + 1;
-            const int chunk = split_chunk_len(total, a.max_chunks, SPLIT_KV_CHUNK_SIZE, a.min_chunk);
-            const long long start_ll = (long long)c * chunk;
-            if (start_ll >= total) {
-                if (!acquire()) { alive = false; break; }
-                publish_header_only(b, hgi, c, kTileFirst | kTileLast | kTileEmpty);
-            } else {
-                const int start = (int)start_ll;
-                const int end = min(start + chunk, total);
-                const unsigned char* kseq = reinterpret_cast<const unsigned char*>(a.k_cache) +
-                    2ll * ((long long)b * a.kv_batch_stride + (long long)hgi * plan.hg * D);
-                const unsigned char* vseq = reinterpret_cast<const unsigned char*>(a.v_cache) +
-                    2ll * ((long long)b * a.kv_batch_stride + (long long)hgi * plan.hg * D);
-                const long long pos_stride = 2ll * a.num_kv_heads * D;
-                for (int pos0 = start; pos0 < end; pos0 += plan.tile) {
-                    if (!acquire()) { alive = false; break; }
-                    const int nvalid = min(plan.tile, end - pos0);
-                    const int nrows = vteb_round_up(nvalid, kBlockPos);
-                    // The newest cache row may be written by the kernel launched just
-                    // before this one: wait for it before touching the final position.
-                    if (!dep_done && pos0 + nvalid >= total) { grid_dependency_wait(); dep_done = true; }
-                    const uint32_t bar = full0 + 8 * stage;
-                    if (lane == 0) {
-                        TileHeader h; h.b = b; h.hgroup = hgi; h.c = c; h.blk0 = (pos0 - start) / kBlockPos;
-                        h.nvalid = nvalid; h.pos0 = pos0; h.pad = 0;
-                        h.flags = (pos0 == start ? kTileFirst : 0) | (pos0 + plan.tile >= end ? kTileLast : 0);
-                        headers[stage] = h;
-                        mbar_arrive_expect_tx(bar, 2u * nrows * plan.row_bytes);
-                    }
-                    __syncwarp();
-                    const uint32_t kdst = smem_u32(stages + (size_t)stage * plan.stage_bytes);
-                    const uint32_t vdst = kdst + plan.tile * plan.row_pitch;
-                    for (int r = lane; r < nrows; r += 32) {
-                        const long long src_pos = min(pos0 + r, end - 1);
-                        bulk_load_row(kdst + r * plan.row_pitch, kseq + src_pos * pos_stride, plan.row_bytes, bar);
-                        bulk_load_row(vdst + r * plan.row_pitch, vseq + src_pos * pos_stride, plan.row_bytes, bar);
-                    }
-                    ++filled;
-                    stage = (stage + 1 == nstages) ? 0 : stage + 1;
-                }
-            }
-            if (!alive) break;
-            // Later items come from the shared ticket, which the previous combine
-            // launch reset: it may only be touched once that launch has completed.
-            if (!dep_done) { grid_dependency_wait(); dep_done = true; }
-            int next = 0;
-            if (lane == 0) next = gridDim.x + atomicAdd(a.ticket, 1);
-            item = __shfl_sync(0xffffffffu, next, 0);
-        }
-        if (alive && acquire()) publish_header_only(0, 0, 0, kTileStop);
-        if (!dep_done) grid_dependency_wait();
-        // Do not leave while copies may still be landing in this CTA's shared
-        // memory: wait (bounded, 100 ms per stage) for the latest "full" phase of
-        // every stage that was handed out.  Stages are used round-robin from 0.
-        for (int s = 0; s < nstages; ++s) {
-            const int fills = filled / nstages + (s < filled % nstages ? 1 : 0);
-            if (fills > 0) mbar_wait_bounded(full0 + 8 * s, (uint32_t)(fills - 1) & 1u, nullptr, 100000000ull);
-        }
-        return;
-    }
-
-    if (warp >= plan.active_warps) return;
-
-    // -------------------------------- consumers --------------------------------
-    const int hh = warp % plan.hg;        // KV head within the group
-    const int sub = warp / plan.hg;       // which of the wph interleaved block streams
-    const int g = lane >> 2, t = lane & 3;
-    const float scale2 = a.scale * kLog2e;
-    constexpr int KS = D / 16;            // k-steps of the QK^T product
-    constexpr int NT = D / 8;             // 8-wide output column tiles
-
-    // Q fragments live in a per-thread column of shared memory: word i of this
-    // thread is q_frag[i * 32]; a thread only ever reads what it wrote itself.
-    uint32_t* q_frag = q_store + warp * (KS * 2 * 32) + lane;
-    float o_acc[NT][2];
-    float m_run = kNeutralM, l_run = 0.f;
-    int stage = 0;
-    uint32_t full_parity = 0;
-    uint32_t merge_parity = 0;
-    bool merge_pending = false;           // previous item's readers may still use the exchange area
-    bool q_ready = false;
-
-    // Lane-constant parts of the ldmatrix addresses.
-    const int k_row = (lane & 7) + ((lane >> 4) << 3);
-    const int k_col = ((lane >> 3) & 1) * 8;
-    const int v_row = (lane & 7) + (((lane >> 3) & 1) << 3);
-    const int v_col = (lane >> 4) * 8;
-
-    for (;;) {
-        if (!mbar_wait_bounded(full0 + 8 * stage, (full_parity >> stage) & 1u, abort_word)) {
-            if (lane == 0) { if (*abort_word == 0) atomicCAS(a.status, 0, kStatusFullTimeout); *abort_word = 1; }
-            return;
-        }
-        full_parity ^= (1u << stage);
-        const TileHeader hd = headers[stage];
-        if (hd.flags & kTileStop) break;
-
-        if (hd.flags & kTileFirst) {
-            m_run = kNeutralM; l_run = 0.f;
-#pragma unroll
-            for (int n = 0; n < NT; ++n) { o_acc[n][0] = 0.f; o_acc[n][1] = 0.f; }
-            if (!q_ready) { grid_dependency_wait(); q_ready = true; }
-            // Row g of the A operand is query head (kv_head * group + g); rows >= group are zero.
-            const int kv_head = hd.hgroup * plan.hg + hh;
-            const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
-                a.q + ((long long)hd.b * a.num_q_heads + (long long)kv_head * group + g) * D);
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                q_frag[(2 * ks) * 32] = (g < group) ? qrow[ks * 8 + t] : 0u;
-                q_frag[(2 * ks + 1) * 32] = (g < group) ? qrow[ks * 8 + 4 + t] : 0u;
-            }
-        }
-
-        if (!(hd.flags & kTileEmpty)) {
-            const uint32_t kt = smem_u32(stages + (size_t)stage * plan.stage_bytes) + hh * D * 2;
-            const uint32_t vt = kt + plan.tile * plan.row_pitch;
-            const int nblk = (hd.nvalid + kBlockPos - 1) / kBlockPos;
-            for (int blk = 0; blk < nblk; ++blk) {
-                if ((hd.blk0 + blk) % plan.wph != sub) continue;
-                const int r0 = blk * kBlockPos;
-                // ---- S = Q K^T for 16 positions: s[0] positions 0..7, s[1] positions 8..15
-                float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-                const uint32_t kaddr = kt + (r0 + k_row) * plan.row_pitch + k_col * 2;
-#pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(kaddr + ks * 32, b0, b1, b2, b3);
-                    const uint32_t qa0 = q_frag[(2 * ks) * 32], qa1 = q_frag[(2 * ks + 1) * 32];
-                    mma_rows0to7(s[0][0], s[0][1], qa0, qa1, b0, b1);
-                    mma_rows0to7(s[1][0], s[1][1], qa0, qa1, b2, b3);
-                }
-                // ---- online softmax (log2 domain); positions past the item's end are masked
-                const int left = hd.nvalid - r0;        // valid positions in this block (may exceed 16)
-                float mx = kNeutralM;
-#pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const bool valid = (n * 8 + 2 * t + j) < left;
-                        s[n][j] = valid ? s[n][j] * scale2 : kNeutralM;
-                        mx = fmaxf(mx, s[n][j]);
-                    }
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m_run, mx);
-                const float corr = fast_exp2(m_run - m_new);
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
-                    l_run *= corr;
-#pragma unroll
-                    for (int n = 0; n < NT; ++n) { o_acc[n][0] *= corr; o_acc[n][1] *= corr; }
-                }
-                m_run = m_new;
-                float p[2][2];
-#pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const bool valid = (n * 8 + 2 * t + j) < left;
-                        p[n][j] = valid ? fast_exp2(s[n][j] - m_new) : 0.f;
-                    }
-                l_run += (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
-                // P = P_hi + P_lo, both fp16: keeps ~22 bits of each probability.
-                uint32_t ph[2], pl[2];
-#pragma unroll
-                for (int n = 0; n < 2; ++n) {
-                    const __half2 hi = __floats2half2_rn(p[n][0], p[n][1]);
-                    const float2 hif = __half22float2(hi);
-                    ph[n] = *reinterpret_cast<const uint32_t*>(&hi);
-                    pl[n] = pack_half2(p[n][0] - hif.x, p[n][1] - hif.y);
-                }
-                // ---- O += P V
-                const uint32_t vaddr = vt + (r0 + v_row) * plan.row_pitch + v_col * 2;
-#pragma unroll
-                for (int np = 0; np < NT / 2; ++np) {
-                    uint32_t v0, v1, v2, v3;
-                    ldmatrix_x4_trans(vaddr + np * 32, v0, v1, v2, v3);
-                    mma_rows0to7(o_acc[2 * np][0], o_acc[2 * np][1], ph[0], ph[1], v0, v1);
-                    mma_rows0to7(o_acc[2 * np + 1][0], o_acc[2 * np + 1][1], ph[0], ph[1], v2, v3);
-                    mma_rows0to7(o_acc[2 * np][0], o_acc[2 * np][1], pl[0], pl[1], v0, v1);
-                    mma_rows0to7(o_acc[2 * np + 1][0], o_acc[2 * np + 1][1], pl[0], pl[1], v2, v3);
-                }
-            }
-        }
-
-        // Hand the stage back to the loader.
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + 8 * stage);
-        stage = (stage + 1 == nstages) ? 0 : stage + 1;
-
-        if (hd.flags & kTileLast) {
-            // ---- exchange (m, l, o) between the warps of each KV head and store the item
-            const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, 2 unused
-            if (merge_pending) {
-                // everyone must have finished reading the previous item's exchange area
-                if (!mbar_wait_bounded(merge_bar0 + 8, (merge_parity >> 1) & 1u, abort_word)) {
-                    if (lane == 0) { if (*abort_word == 0) atomicCAS(a.status, 0, kStatusMergeTimeout); *abort_word = 1; }
-                    return;
-                }
-                merge_parity ^= 2u;
-            }
-            float l_quad = l_run;
-            l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 1);
-            l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 2);
-            if (g < group) {
-                float* dst = merge + ((size_t)warp * group + g) * pitch;
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-                    *reinterpret_cast<float2*>(dst + n * 8 + 2 * t) = make_float2(o_acc[n][0], o_acc[n][1]);
-                if (t == 0) { dst[D + 4] = m_run; dst[D + 5] = l_quad; }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(merge_bar0);
-            if (!mbar_wait_bounded(merge_bar0, merge_parity & 1u, abort_word)) {
-                if (lane == 0) { if (*abort_word == 0) atomicCAS(a.status, 0, kStatusMergeTimeout); *abort_word = 1; }
-                return;
-            }
-            merge_parity ^= 1u;
-
-            const bool empty = (hd.flags & kTileEmpty) != 0;
-            const int nthreads = plan.active_warps * 32;
-            const int heads_item = plan.hg * group;                    // query heads of this item
-            const int q_head0 = hd.hgroup * heads_item;
-            const long long stat0 = ((long long)hd.b * a.num_q_heads + q_head0) * a.max_chunks + hd.c;
-            if (!empty || (a.flags & kFlagWriteEmptyO)) {
-                for (int idx = threadIdx.x; idx < heads_item * (D / 4); idx += nthreads) {
-                    const int hq = idx / (D / 4), d4 = idx - hq * (D / 4);
-                    const int kvh = hq / group, row = hq - kvh * group;
-                    float mm = kNeutralM;
-                    for (int w = 0; w < plan.wph; ++w)
-                        mm = fmaxf(mm, merge[((size_t)(w * plan.hg + kvh) * group + row) * pitch + D + 4]);
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int w = 0; w < plan.wph; ++w) {
-                        const float* src = merge + ((size_t)(w * plan.hg + kvh) * group + row) * pitch;
-                        const float wt = fast_exp2(src[D + 4] - mm);
-                        const float4 x = *reinterpret_cast<const float4*>(src + d4 * 4);
-                        acc.x = fmaf(x.x, wt, acc.x); acc.y = fmaf(x.y, wt, acc.y);
-                        acc.z = fmaf(x.z, wt, acc.z); acc.w = fmaf(x.w, wt, acc.w);
-                    }
-                    float* out = a.partial_o + (stat0 + (long long)hq * a.max_chunks) * D + d4 * 4;
-                    *reinterpret_cast<float4*>(out) = acc;
-                }
-            }
-            for (int hq = threadIdx.x; hq < heads_item; hq += nthreads) {
-                const int kvh = hq / group, row = hq - kvh * group;
-                float mm = kNeutralM, ll = 0.f;
-                for (int w = 0; w < plan.wph; ++w)
-                    mm = fmaxf(mm, merge[((size_t)(w * plan.hg + kvh) * group + row) * pitch + D + 4]);
-                for (int w = 0; w < plan.wph; ++w) {
-                    const float* src = merge + ((size_t)(w * plan.hg + kvh) * group + row) * pitch;
-                    ll += src[D + 5] * fast_exp2(src[D + 4] - mm);
-                }
-                a.partial_m[stat0 + (long long)hq * a.max_chunks] = empty ? kNeutralM : mm * kLn2;
-                a.partial_l[stat0 + (long long)hq * a.max_chunks] = empty ? 0.f : ll;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(merge_bar0 + 8);
-            merge_pending = true;
-        }
-    }
-}
-
-#define VTEB_FAST_PARTIAL(NAME, DIM)                                                                  \
-    extern "C" __global__ void __launch_bounds__(kFastThreads, 1) NAME(                               \
-        const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
-        const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
-        float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
-        int num_kv_heads, int head_dim, float scale, const int* __restrict__ kv_cache_offset_ptr,     \
-        int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
-        const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status)        \
-    {                                                                                                 \
-        FastArgs a;                                                                                   \
-        a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
-        a.partial_m = partial_m; a.partial_l = partial_l; a.partial_o = partial_o;                    \
-        a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.scale = scale;                  \
-        a.kv_offsets = kv_cache_offset_ptr; a.kv_batch_stride = kv_batch_stride;                      \
-        a.max_chunks = max_chunks; a.batch = batch; a.min_chunk = min_chunk; a.flags = flags;         \
-        a.seq_order = seq_order; a.ticket = ticket; a.status = status;                                \
-        (void)head_dim;                                                                               \
-        fast_partial_body<DIM>(a);                                                                    \
-    }
-
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256)
+#include "split_kv_fast.cuh"

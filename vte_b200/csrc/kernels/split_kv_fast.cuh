@@ -1,0 +1,532 @@
+// Fast split kernel of the decode-attention path (included by decode_attention.cu).
+//
+// grid (n_ctas, 1, 1) persistent, block 320 = eight consumer warps + two loader
+// warps, dynamic shared memory from make_fast_plan().  A work item is one split
+// of one sequence for one group of `hg` KV heads; item t maps to
+// (sequence rank t / (n_hgroups * C), head group, split).  CTA i starts with
+// item i and draws the following ones from `*ticket` (gridDim.x + atomicAdd).
+//
+// Loader warp K (warp 8): for every tile of `tile` positions it waits for a free
+// stage, writes the tile header, and copies the K rows (row_bytes contiguous
+// bytes covering the group's heads) with 16-byte asynchronous copies, one
+// 512-byte piece per warp instruction, into rows padded by 16 bytes.  Loader
+// warp V (warp 9) follows the headers and copies the V rows.  The copies'
+// completion is counted on the stage's "full" mbarrier.  Rows past the end of
+// the item are filled from the item's last row so that every row a consumer
+// touches holds finite numbers.
+//
+// Consumer warp w: KV head (w % hg) of the group, every wph-th 16-position
+// block.  Per block: S = Q K^T with mma.sync m16n8k16 (Q rows are the query
+// heads of the KV head, K fragments via ldmatrix), online softmax in the log2
+// domain on the accumulator fragment, P split into an fp16 high and low part,
+// O += P V with V fragments via ldmatrix.trans.  At the end of an item the
+// warps of a KV head exchange (m, l, o) through shared memory and the merged
+// state is stored to partial_m / partial_l / partial_o.
+//
+// Every wait is bounded; a wait that gives up stores a code in `*status`,
+// raises the CTA's abort word, and the CTA's warps return (the loader warps
+// first wait for their own outstanding copies).
+#pragma once
+
+struct FastArgs {
+    const __half* q; const __half* k_cache; const __half* v_cache;
+    float* partial_m; float* partial_l; float* partial_o;
+    int num_q_heads, num_kv_heads; float scale;
+    const int* kv_offsets; long long kv_batch_stride; int max_chunks;
+    int batch, min_chunk, flags; const int* seq_order; int* ticket; int* status;
+};
+
+constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
+
+// Shared-memory control block (first kCtrlBytes of dynamic shared memory).
+constexpr int kBarFull = 0;                        // 8 barriers
+constexpr int kBarEmpty = 8 * kMaxStages;          // 8 barriers
+constexpr int kBarHeader = 16 * kMaxStages;        // 8 barriers: header published (K loader -> V loader)
+constexpr int kBarMerge = 24 * kMaxStages;         // 2 barriers
+constexpr int kAbortOffset = 256;
+constexpr int kHeaderOffset = 512;
+
+__device__ __forceinline__ void raise_abort(volatile int* abort_word, int* status, int code) {
+    if ((threadIdx.x & 31) == 0) {
+        if (*abort_word == 0) atomicCAS(status, 0, code);
+        *abort_word = 1;
+    }
+}
+
+// Copies `nrows` (a multiple of 8) position rows of `row_bytes` <= 1024 bytes each
+// (this lane's 16-byte pieces of them) from global to padded shared rows; rows at
+// or past `nvalid` are taken from `src_last`.  `src`, `src_last` and `dst` already
+// include the lane's 16-byte offset.  Eight rows' addresses are formed first and
+// their copies issued back to back: an asynchronous copy holds its address
+// registers until the load/store unit has picked it up, so a loop that bumps one
+// pointer per copy stalls for that latency on every row (measured: ~230 cycles
+// per row instead of ~16).
+__device__ __forceinline__ void copy_rows_async(const unsigned char* src, const unsigned char* src_last,
+                                                uint32_t dst, int nrows, int nvalid, int row_bytes,
+                                                int row_pitch, long long pos_stride, int lane) {
+    const bool piece0 = lane * 16 < row_bytes;                    // bytes [0, 512) of the row
+    const bool piece1 = 512 + lane * 16 < row_bytes;              // bytes [512, 1024)
+    for (int r0 = 0; r0 < nrows; r0 += 8) {
+        const unsigned char* s[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = (r0 + i < nvalid) ? src + (long long)i * pos_stride : src_last;
+        if (piece0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch, s[i]);
+        }
+        if (piece1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch + 512, s[i] + 512);
+        }
+        src += 8 * pos_stride;
+        dst += 8 * row_pitch;
+    }
+}
+
+struct ItemGeometry {
+    int b, hgroup, c, start, end;   // end <= start: empty item
+};
+
+__device__ __forceinline__ ItemGeometry decode_item(const FastArgs& a, const FastPlan& plan, int item) {
+    ItemGeometry g;
+    const int items_per_seq = plan.n_hgroups * a.max_chunks;
+    const int rank = item / items_per_seq;
+    const int rem = item - rank * items_per_seq;
+    g.hgroup = rem / a.max_chunks;
+    g.c = rem - g.hgroup * a.max_chunks;
+    g.b = a.seq_order ? a.seq_order[rank] : rank;
+    const int total = a.kv_offsets[g.b] + 1;
+    const int chunk = split_chunk_len(total, a.max_chunks, SPLIT_KV_CHUNK_SIZE, a.min_chunk);
+    const long long start = (long long)g.c * chunk;
+    if (start >= total) { g.start = total; g.end = total; }
+    else { g.start = (int)start; g.end = min(g.start + chunk, total); }
+    return g;
+}
+
+template <int D>
+__device__ __forceinline__ void fast_partial_body(const FastArgs& a)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const FastPlan plan = make_fast_plan(a.num_q_heads, a.num_kv_heads, D);
+    const int group = a.num_q_heads / a.num_kv_heads;
+
+    volatile int* abort_word = reinterpret_cast<volatile int*>(smem_raw + kAbortOffset);
+    TileHeader* headers = reinterpret_cast<TileHeader*>(smem_raw + kHeaderOffset);
+    float* merge = reinterpret_cast<float*>(smem_raw + kCtrlBytes);
+    uint32_t* q_store = reinterpret_cast<uint32_t*>(smem_raw + kCtrlBytes + plan.merge_bytes);
+    unsigned char* stages = smem_raw + kCtrlBytes + plan.merge_bytes + plan.q_bytes;
+
+    const uint32_t bar0 = smem_u32(smem_raw);
+    const uint32_t full0 = bar0 + kBarFull * 1, empty0 = bar0 + kBarEmpty, hdr0 = bar0 + kBarHeader;
+    const uint32_t merge_bar0 = bar0 + kBarMerge;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nstages = plan.nstages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(full0 + 8 * s, 65);        // 64 asynchronous-copy arrivals + the header writer
+            mbar_init(empty0 + 8 * s, plan.active_warps);
+            mbar_init(hdr0 + 8 * s, 1);
+        }
+        mbar_init(merge_bar0, plan.active_warps);
+        mbar_init(merge_bar0 + 8, plan.active_warps);
+        *abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    grid_launch_dependents();
+
+    const int total_items = a.batch * plan.n_hgroups * a.max_chunks;
+    const long long pos_stride = 2ll * a.num_kv_heads * D;      // bytes between positions
+
+    // ===================================================================== K loader
+    if (warp == kLoaderWarpK) {
+        int stage = 0, filled = 0;
+        uint32_t empty_parity = 0;
+        bool dep_done = false;
+        int item = blockIdx.x;
+        int trace_tile = 0;
+        bool alive = true;
+        while (alive) {
+            const bool stop = item >= total_items;
+            ItemGeometry g;
+            if (!stop) g = decode_item(a, plan, item);
+            const int ntiles = stop ? 1 : max(1, (g.end - g.start + plan.tile - 1) / plan.tile);
+            for (int t = 0; t < ntiles; ++t) {
+                VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 0);
+                if (filled >= nstages) {
+                    if (!mbar_wait_bounded(empty0 + 8 * stage, (empty_parity >> stage) & 1u, abort_word)) {
+                        raise_abort(abort_word, a.status, kStatusEmptyTimeout);
+                        alive = false;
+                        break;
+                    }
+                    empty_parity ^= (1u << stage);
+                }
+                VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 1);
+                const uint32_t bar = full0 + 8 * stage;
+                const bool empty_item = !stop && g.end <= g.start;
+                const int pos0 = stop ? 0 : g.start + t * plan.tile;
+                const int nvalid = (stop || empty_item) ? 0 : min(plan.tile, g.end - pos0);
+                // The newest cache row may be written by the kernel launched just before
+                // this one: wait for that kernel before touching the sequence's last position.
+                if (!dep_done && !stop && !empty_item && g.end == a.kv_offsets[g.b] + 1 && pos0 + nvalid >= g.end) {
+                    grid_dependency_wait();
+                    dep_done = true;
+                }
+                if (lane == 0) {
+                    TileHeader h;
+                    h.b = stop ? 0 : g.b; h.hgroup = stop ? 0 : g.hgroup; h.c = stop ? 0 : g.c;
+                    h.blk0 = t * (plan.tile / kBlockPos); h.nvalid = nvalid; h.pos0 = pos0;
+                    h.last_pos = stop ? 0 : g.end - 1;
+                    h.flags = stop ? kTileStop
+                                   : ((t == 0 ? kTileFirst : 0) | (t == ntiles - 1 ? kTileLast : 0) | (empty_item ? kTileEmpty : 0));
+                    headers[stage] = h;
+                    mbar_arrive(hdr0 + 8 * stage);
+                    mbar_arrive(bar);
+                }
+                if (nvalid > 0) {
+                    const int nrows = vteb_round_up(nvalid, kBlockPos);
+                    const unsigned char* src = reinterpret_cast<const unsigned char*>(a.k_cache) +
+                        2ll * ((long long)g.b * a.kv_batch_stride + (long long)g.hgroup * plan.hg * D) +
+                        (long long)pos0 * pos_stride + lane * 16;
+                    const unsigned char* src_last = src + (long long)(g.end - 1 - pos0) * pos_stride;
+                    const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + lane * 16;
+                    copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
+                    async_copy_arrive(bar);
+                } else {
+                    mbar_arrive(bar);      // no copies belong to this tile
+                }
+                VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 2);
+                ++trace_tile;
+                ++filled;
+                stage = (stage + 1 == nstages) ? 0 : stage + 1;
+            }
+            if (stop || !alive) break;
+            // Later items come from the shared ticket, which the previous combine
+            // launch reset: it may only be touched once that launch has completed.
+            if (!dep_done) { grid_dependency_wait(); dep_done = true; }
+            int next = 0;
+            if (lane == 0) next = gridDim.x + atomicAdd(a.ticket, 1);
+            item = __shfl_sync(0xffffffffu, next, 0);
+        }
+        if (!dep_done) grid_dependency_wait();
+        asm volatile("cp.async.wait_all;" ::: "memory");   // own copies have landed before the warp leaves
+        return;
+    }
+
+    // ===================================================================== V loader
+    if (warp == kLoaderWarpV) {
+        int stage = 0;
+        uint32_t hdr_parity = 0;
+        bool dep_done = false;
+        for (;;) {
+            if (!mbar_wait_bounded(hdr0 + 8 * stage, (hdr_parity >> stage) & 1u, abort_word)) break;
+            hdr_parity ^= (1u << stage);
+            const TileHeader hd = headers[stage];
+            const uint32_t bar = full0 + 8 * stage;
+            if (hd.nvalid > 0) {
+                if (!dep_done && hd.last_pos == a.kv_offsets[hd.b] && hd.pos0 + hd.nvalid > hd.last_pos) {
+                    grid_dependency_wait();
+                    dep_done = true;
+                }
+                const int nrows = vteb_round_up(hd.nvalid, kBlockPos);
+                const unsigned char* src = reinterpret_cast<const unsigned char*>(a.v_cache) +
+                    2ll * ((long long)hd.b * a.kv_batch_stride + (long long)hd.hgroup * plan.hg * D) +
+                    (long long)hd.pos0 * pos_stride + lane * 16;
+                const unsigned char* src_last = src + (long long)(hd.last_pos - hd.pos0) * pos_stride;
+                const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_pitch + lane * 16;
+                copy_rows_async(src, src_last, dst, nrows, hd.nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
+                async_copy_arrive(bar);
+            } else {
+                mbar_arrive(bar);
+            }
+            if (hd.flags & kTileStop) break;
+            stage = (stage + 1 == nstages) ? 0 : stage + 1;
+        }
+        if (!dep_done) grid_dependency_wait();
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        return;
+    }
+
+    if (warp >= plan.active_warps) return;
+
+    // ===================================================================== consumers
+    const int hh = warp % plan.hg;        // KV head within the group
+    const int sub = warp / plan.hg;       // which of the wph interleaved block streams
+    const int wph_mask = plan.wph - 1;    // wph is a power of two
+    const int g = lane >> 2, t = lane & 3;
+    const float scale2 = a.scale * kLog2e;
+    constexpr int KS = D / 16;            // k-steps of the QK^T product
+    constexpr int NT = D / 8;             // 8-wide output column tiles
+    const int blocks_per_tile = plan.tile / kBlockPos;
+
+    // Q operand fragments of this warp's KV head: word i of lane L at q_frag[i * 32].
+    // Every warp of the head writes the same values; they are rewritten only after
+    // the item's merge barrier, when no warp of the CTA still reads the old ones.
+    uint32_t* q_frag = q_store + hh * (KS * 2 * 32) + lane;
+    auto load_q = [&](int b, int hgroup) {
+        const int kv_head = hgroup * plan.hg + hh;
+        const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+            a.q + ((long long)b * a.num_q_heads + (long long)kv_head * group + g) * D);
+        uint32_t tmp[KS * 2];
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            tmp[2 * ks] = (g < group) ? qrow[ks * 8 + t] : 0u;
+            tmp[2 * ks + 1] = (g < group) ? qrow[ks * 8 + 4 + t] : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < KS * 2; ++i) q_frag[i * 32] = tmp[i];
+        __syncwarp();
+    };
+
+    float o_acc[NT][2];
+    float m_run = kNeutralM, l_run = 0.f;
+    int stage = 0;
+    uint32_t full_parity = 0, merge_parity = 0;
+    bool merge_pending = false;           // previous item's readers may still use the exchange area
+    bool first_item = true;
+
+    // Lane-constant parts of the ldmatrix addresses.
+    const int k_lane_off = ((lane & 7) + ((lane >> 4) << 3)) * plan.row_pitch + (((lane >> 3) & 1) * 8 + hh * D) * 2;
+    const int v_lane_off = ((lane & 7) + (((lane >> 3) & 1) << 3)) * plan.row_pitch + ((lane >> 4) * 8 + hh * D) * 2;
+    const int v_tile_off = plan.tile * plan.row_pitch;
+
+    // The first item is known without the loader: fetch its Q while the first tile is in flight.
+    grid_dependency_wait();
+    if (blockIdx.x < total_items) {
+        const int items_per_seq = plan.n_hgroups * a.max_chunks;
+        const int rank = blockIdx.x / items_per_seq;
+        const int hgroup = (blockIdx.x - rank * items_per_seq) / a.max_chunks;
+        load_q(a.seq_order ? a.seq_order[rank] : rank, hgroup);
+    }
+
+    int trace_tile = 0;
+    for (;;) {
+        VTEB_TRACE_EVENT(warp, trace_tile, 0);
+        if (!mbar_wait_bounded(full0 + 8 * stage, (full_parity >> stage) & 1u, abort_word)) {
+            raise_abort(abort_word, a.status, kStatusFullTimeout);
+            return;
+        }
+        full_parity ^= (1u << stage);
+        VTEB_TRACE_EVENT(warp, trace_tile, 1);
+        const TileHeader* hd = headers + stage;
+        const int flags = hd->flags;
+        if (flags & kTileStop) break;
+        // Copy what is needed later: the loader may rewrite the header once every
+        // consumer warp has released the stage.
+        const int item_b = hd->b, item_hgroup = hd->hgroup, item_c = hd->c;
+        const int nvalid = hd->nvalid, blk0 = hd->blk0;
+
+        if (flags & kTileFirst) {
+            m_run = kNeutralM; l_run = 0.f;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) { o_acc[n][0] = 0.f; o_acc[n][1] = 0.f; }
+            if (!first_item) load_q(item_b, item_hgroup);
+            first_item = false;
+        }
+
+        const uint32_t tile_base = smem_u32(stages + (size_t)stage * plan.stage_bytes);
+        for (int blk = 0; blk < blocks_per_tile; ++blk) {
+            const int r0 = blk * kBlockPos;
+            if (r0 >= nvalid) break;
+            if (((blk0 + blk) & wph_mask) != sub) continue;
+            // ---- S = Q K^T: s[0] positions 0..7, s[1] positions 8..15; two accumulation
+            // chains each; K fragments are fetched eight k-steps at a time
+            const uint32_t kaddr = tile_base + r0 * plan.row_pitch + k_lane_off;
+            float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, s_alt[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+            constexpr int KC = KS < 8 ? KS : 8;
+#pragma unroll
+            for (int kc = 0; kc < KS; kc += KC) {
+                uint32_t kf[KC][4];
+#pragma unroll
+                for (int i = 0; i < KC; ++i) ldmatrix_x4(kaddr + (kc + i) * 32, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
+#pragma unroll
+                for (int i = 0; i < KC; i += 2) {
+                    const int ks = kc + i;
+                    const uint32_t qa0 = q_frag[(2 * ks) * 32], qa1 = q_frag[(2 * ks + 1) * 32];
+                    const uint32_t qb0 = q_frag[(2 * ks + 2) * 32], qb1 = q_frag[(2 * ks + 3) * 32];
+                    mma_rows0to7(s[0][0], s[0][1], qa0, qa1, kf[i][0], kf[i][1]);
+                    mma_rows0to7(s[1][0], s[1][1], qa0, qa1, kf[i][2], kf[i][3]);
+                    mma_rows0to7(s_alt[0][0], s_alt[0][1], qb0, qb1, kf[i + 1][0], kf[i + 1][1]);
+                    mma_rows0to7(s_alt[1][0], s_alt[1][1], qb0, qb1, kf[i + 1][2], kf[i + 1][3]);
+                }
+            }
+            // ---- V fragments do not depend on the softmax: fetch the first 64 columns now
+            const uint32_t vaddr = tile_base + v_tile_off + r0 * plan.row_pitch + v_lane_off;
+            constexpr int VC = 4;                 // ldmatrix.x4.trans per chunk = 64 output columns
+            constexpr int NVC = NT / (2 * VC);    // chunks
+            uint32_t vf[2][VC][4];
+#pragma unroll
+            for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr + i * 32, vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
+            // ---- online softmax (log2 domain); positions past the item's end are masked
+            const int left = nvalid - r0;         // valid positions in this block (may exceed 16)
+            float mx = kNeutralM;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const bool valid = (n * 8 + 2 * t + j) < left;
+                    s[n][j] = valid ? (s[n][j] + s_alt[n][j]) * scale2 : kNeutralM;
+                    mx = fmaxf(mx, s[n][j]);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const float corr = fast_exp2(m_run - m_new);
+            if (__any_sync(0xffffffffu, corr != 1.f)) {
+                l_run *= corr;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) { o_acc[n][0] *= corr; o_acc[n][1] *= corr; }
+            }
+            m_run = m_new;
+            float p[2][2];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const bool valid = (n * 8 + 2 * t + j) < left;
+                    p[n][j] = valid ? fast_exp2(s[n][j] - m_new) : 0.f;
+                }
+            l_run += (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+            // P = P_hi + P_lo, both fp16: keeps ~22 bits of each probability.
+            uint32_t ph[2], pl[2];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const __half2 hi = __floats2half2_rn(p[n][0], p[n][1]);
+                const float2 hif = __half22float2(hi);
+                ph[n] = *reinterpret_cast<const uint32_t*>(&hi);
+                pl[n] = pack_half2(p[n][0] - hif.x, p[n][1] - hif.y);
+            }
+            // ---- O += P V, 64 columns per chunk; the next chunk's fragments load meanwhile
+#pragma unroll
+            for (int ch = 0; ch < NVC; ++ch) {
+                if (ch + 1 < NVC) {
+#pragma unroll
+                    for (int i = 0; i < VC; ++i)
+                        ldmatrix_x4_trans(vaddr + ((ch + 1) * VC + i) * 32, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
+                                          vf[(ch + 1) & 1][i][2], vf[(ch + 1) & 1][i][3]);
+                }
+#pragma unroll
+                for (int i = 0; i < VC; ++i) {
+                    const int n = 2 * (ch * VC + i);
+                    mma_rows0to7(o_acc[n][0], o_acc[n][1], ph[0], ph[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
+                    mma_rows0to7(o_acc[n + 1][0], o_acc[n + 1][1], ph[0], ph[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
+                }
+#pragma unroll
+                for (int i = 0; i < VC; ++i) {
+                    const int n = 2 * (ch * VC + i);
+                    mma_rows0to7(o_acc[n][0], o_acc[n][1], pl[0], pl[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
+                    mma_rows0to7(o_acc[n + 1][0], o_acc[n + 1][1], pl[0], pl[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
+                }
+            }
+        }
+
+        // Hand the stage back to the loader.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+        VTEB_TRACE_EVENT(warp, trace_tile, 2);
+        ++trace_tile;
+
+        if (flags & kTileLast) {
+            stage = (stage + 1 == nstages) ? 0 : stage + 1;
+            // ---- exchange (m, l, o) between the warps of each KV head and store the item
+            const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, 2 unused
+            if (merge_pending) {
+                // everyone must have finished reading the previous item's exchange area
+                if (!mbar_wait_bounded(merge_bar0 + 8, (merge_parity >> 1) & 1u, abort_word)) {
+                    raise_abort(abort_word, a.status, kStatusMergeTimeout);
+                    return;
+                }
+                merge_parity ^= 2u;
+            }
+            float l_quad = l_run;
+            l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 1);
+            l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 2);
+            if (g < group) {
+                float* dst = merge + ((size_t)warp * group + g) * pitch;
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+                    *reinterpret_cast<float2*>(dst + n * 8 + 2 * t) = make_float2(o_acc[n][0], o_acc[n][1]);
+                if (t == 0) { dst[D + 4] = m_run; dst[D + 5] = l_quad; }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(merge_bar0);
+            if (!mbar_wait_bounded(merge_bar0, merge_parity & 1u, abort_word)) {
+                raise_abort(abort_word, a.status, kStatusMergeTimeout);
+                return;
+            }
+            merge_parity ^= 1u;
+
+            // One (KV head, query row) pair per warp pass: all lanes derive the pair's
+            // weights from broadcast reads, then each lane merges its float4 columns.
+            const bool empty = (flags & kTileEmpty) != 0;
+            const int heads_item = plan.hg * group;                    // query heads of this item
+            const long long stat0 = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * heads_item) * a.max_chunks + item_c;
+            const bool write_o = !empty || (a.flags & kFlagWriteEmptyO);
+            for (int hq = warp; hq < heads_item; hq += plan.active_warps) {
+                const int kvh = hq / group, row = hq - kvh * group;
+                const float* src0 = merge + ((size_t)kvh * group + row) * pitch;        // warp (0 * hg + kvh)
+                const size_t wstride = (size_t)plan.hg * group * pitch;                  // next warp of the same head
+                float mm = kNeutralM;
+                for (int w = 0; w < plan.wph; ++w) mm = fmaxf(mm, src0[w * wstride + D + 4]);
+                float ll = 0.f;
+                float4 acc[(D + 127) / 128];
+#pragma unroll
+                for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int w = 0; w < plan.wph; ++w) {
+                    const float* src = src0 + w * wstride;
+                    const float wt = fast_exp2(src[D + 4] - mm);
+                    ll = fmaf(src[D + 5], wt, ll);
+#pragma unroll
+                    for (int i = 0; i < (D + 127) / 128; ++i) {
+                        if (D >= 128 || lane < D / 4) {
+                            const float4 x = *reinterpret_cast<const float4*>(src + i * 128 + lane * 4);
+                            acc[i].x = fmaf(x.x, wt, acc[i].x); acc[i].y = fmaf(x.y, wt, acc[i].y);
+                            acc[i].z = fmaf(x.z, wt, acc[i].z); acc[i].w = fmaf(x.w, wt, acc[i].w);
+                        }
+                    }
+                }
+                const long long stat = stat0 + (long long)hq * a.max_chunks;
+                if (write_o) {
+#pragma unroll
+                    for (int i = 0; i < (D + 127) / 128; ++i)
+                        if (D >= 128 || lane < D / 4)
+                            *reinterpret_cast<float4*>(a.partial_o + stat * D + i * 128 + lane * 4) = acc[i];
+                }
+                if (lane == 0) {
+                    a.partial_m[stat] = empty ? kNeutralM : mm * kLn2;
+                    a.partial_l[stat] = empty ? 0.f : ll;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(merge_bar0 + 8);
+            merge_pending = true;
+        } else {
+            stage = (stage + 1 == nstages) ? 0 : stage + 1;
+        }
+    }
+}
+
+#define VTEB_FAST_PARTIAL(NAME, DIM)                                                                  \
+    extern "C" __global__ void __launch_bounds__(kFastThreads, 1) NAME(                               \
+        const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
+        const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
+        float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
+        int num_kv_heads, int head_dim, float scale, const int* __restrict__ kv_cache_offset_ptr,     \
+        int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
+        const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status)        \
+    {                                                                                                 \
+        FastArgs a;                                                                                   \
+        a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
+        a.partial_m = partial_m; a.partial_l = partial_l; a.partial_o = partial_o;                    \
+        a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.scale = scale;                  \
+        a.kv_offsets = kv_cache_offset_ptr; a.kv_batch_stride = kv_batch_stride;                      \
+        a.max_chunks = max_chunks; a.batch = batch; a.min_chunk = min_chunk; a.flags = flags;         \
+        a.seq_order = seq_order; a.ticket = ticket; a.status = status;                                \
+        (void)head_dim;                                                                               \
+        fast_partial_body<DIM>(a);                                                                    \
+    }
+
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256)

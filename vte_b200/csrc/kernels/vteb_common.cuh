@@ -10,14 +10,18 @@
 namespace vteb {
 
 constexpr int kConsumerWarps = 8;
-constexpr int kProducerWarp = kConsumerWarps;            // warp index of the loader warp
-constexpr int kFastThreads = (kConsumerWarps + 1) * 32;  // 288
+constexpr int kLoaderWarpK = kConsumerWarps;             // loads K rows, owns the work queue
+constexpr int kLoaderWarpV = kConsumerWarps + 1;         // loads V rows, follows the K loader's headers
+constexpr int kFastThreads = (kConsumerWarps + 2) * 32;  // 320
 constexpr int kMaxStages = 8;
 constexpr int kBlockPos = 16;                            // positions per mma step
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kNeutralM = -1e30f;                      // reference's "empty split" maximum
-constexpr int kSmemBudget = 227 * 1024;                  // opt-in dynamic shared memory per CTA
+#ifndef VTEB_SMEM_BUDGET_KB
+#define VTEB_SMEM_BUDGET_KB 227
+#endif
+constexpr int kSmemBudget = VTEB_SMEM_BUDGET_KB * 1024;  // dynamic shared memory the split kernel may use
 
 // Status word written by a kernel that gave up on a wait.  The host reads it
 // after synchronising; zero means every wait completed.
@@ -40,7 +44,7 @@ struct TileHeader {
     int nvalid;   // positions of this tile that belong to the item
     int flags;
     int pos0;     // absolute position of the tile's first row
-    int pad;
+    int last_pos; // last position of the item (rows past it are filled from this one)
 };
 
 // Everything the launch geometry depends on.  Computed identically on the host
@@ -55,7 +59,7 @@ struct FastPlan {
     int row_pitch;     // row_bytes + 16: keeps ldmatrix row addresses on distinct banks
     int stage_bytes;   // K tile + V tile
     int merge_bytes;   // per-warp (m, l, o) exchange area
-    int q_bytes;       // per-thread Q fragment store (keeps the fragments out of registers)
+    int q_bytes;       // Q operand fragments in shared memory (keeps them out of registers)
     int nstages;
     int smem_bytes;    // total dynamic shared memory
     int ok;            // 0 when the geometry is outside what the fast kernel covers
@@ -92,7 +96,7 @@ __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_h
     p.tile = tile;
     p.stage_bytes = vteb_round_up(2 * tile * p.row_pitch, 128);
     p.merge_bytes = vteb_round_up(p.active_warps * group * (head_dim + kMergePad) * 4, 128);
-    p.q_bytes = kConsumerWarps * (head_dim / 8) * 32 * 4;
+    p.q_bytes = hg * (head_dim / 8) * 32 * 4;   // one fragment image per KV head, shared by its warps
     int left = kSmemBudget - kCtrlBytes - p.merge_bytes - p.q_bytes;
     int n = left / p.stage_bytes;
     if (n > kMaxStages) n = kMaxStages;
@@ -120,12 +124,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -138,8 +136,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+#ifndef VTEB_WAIT_MODE
+#define VTEB_WAIT_MODE 0
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
+#if VTEB_WAIT_MODE == 1
+    asm volatile(
+        "{\n"
+        "  .reg .pred p;\n"
+        "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "  selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(20000u)
+        : "memory");
+#else
     asm volatile(
         "{\n"
         "  .reg .pred p;\n"
@@ -149,34 +161,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
+#if VTEB_WAIT_MODE == 2
+    if (!done) __nanosleep(200);
+#endif
+#endif
     return done != 0;
 }
 
-// Waits for a barrier phase for at most `limit_ns` of wall time, also giving
-// up as soon as another warp of the CTA has raised `*abort_word` (pass nullptr
-// to ignore it).  Returns false when it gave up; the caller then records a
-// status code and leaves.
+// Waits for a barrier phase for at most `limit_cycles` SM clock cycles
+// (4e9 is about two seconds), also giving up as soon as another warp of the
+// CTA has raised `*abort_word` (pass nullptr to ignore it).  Returns false when
+// it gave up; the caller then records a status code and leaves.  The SM-local
+// cycle counter is used because reading %globaltimer costs microseconds.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word,
-                                                  uint64_t limit_ns = 2000000000ull) {
+                                                  long long limit_cycles = 4000000000ll) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long t0 = clock64();
     for (uint32_t spin = 1; spin < (1u << 30); ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 0xFF) == 0) {
+        if ((spin & 0x3F) == 0) {
             if (abort_word != nullptr && *abort_word != 0) return false;
-            if (global_timer_ns() - t0 > limit_ns) return false;
+            if (clock64() - t0 > limit_cycles) return false;
         }
     }
     return false;
 }
 
-// One row of K or V: global -> this CTA's shared memory, completion counted on
-// an mbarrier.  Source, destination and size are multiples of 16 bytes.
-__device__ __forceinline__ void bulk_load_row(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
+// 16 bytes global -> shared through the asynchronous copy path (L2 only, no
+// register staging).  Measured on B200: one warp issuing these sustains
+// ~6.4 TB/s across 148 SMs, while cp.async.bulk requests of one 512-byte cache
+// row each are limited by the per-request rate of the bulk-copy engine
+// (~2.3 TB/s at 512 B, full rate only from 2 KB per request), and the padded
+// row layout that keeps ldmatrix conflict-free rules out larger bulk requests.
+__device__ __forceinline__ void async_copy_16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+// Makes the calling thread's earlier async_copy_16 operations count as one
+// arrival on the barrier once they have all landed.
+__device__ __forceinline__ void async_copy_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void grid_dependency_wait() {
@@ -203,7 +227,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
 // only the two accumulators of row (lane / 4) are kept.
 __device__ __forceinline__ void mma_rows0to7(float& d0, float& d1, uint32_t a_lo, uint32_t a_hi, uint32_t b0, uint32_t b1) {
     float u0, u1;
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%11};"
         : "+f"(d0), "+f"(d1), "=f"(u0), "=f"(u1)
