@@ -136,7 +136,7 @@ typedef struct vteb_fast_plan {
     int smem_bytes;    /* dynamic shared memory of the split kernel */
     int threads;       /* block size of the split kernel */
     int combine_dsplit;/* CTAs per (sequence, query head) of the combine kernel */
-    int combine_smem_bytes; /* for max_chunks = 1; add 4 bytes per extra chunk */
+    int combine_smem_bytes; /* per split, up to 256 splits: min(max_chunks, 256) * this */
 } vteb_fast_plan;
 int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
 

@@ -244,6 +244,6 @@ class SplitKVAttentionDispatcher:
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
         dsplit = plan.combine_dsplit
         combine_args = reduce_args + [ci(dsplit), vp(self._work.ptr)]
-        combine_smem = C * 4 + 8 * (D // dsplit) * 4
+        combine_smem = min(C, 256) * 4
         combine = (reduce_fn, combine_args, (batch * Hq * dsplit, 1, 1), (256, 1, 1), combine_smem)
         return [append, partial, combine]

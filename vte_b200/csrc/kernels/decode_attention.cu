@@ -28,11 +28,33 @@ using namespace vteb;
 // clock64() at a few points per tile into a global buffer.  Compiled out otherwise.
 #ifdef VTEB_TRACE
 __device__ long long vteb_trace_buf[9 * 64 * 4];
+__device__ unsigned long long vteb_trace_cta[1024 * 4];   // per CTA: %globaltimer at entry / first tile / last release / exit
+__device__ __forceinline__ unsigned long long vteb_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define VTEB_TRACE_CTA(slot_) \
+    do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) vteb_trace_cta[blockIdx.x * 4 + (slot_)] = vteb_global_ns(); } while (0)
+// per launch: [layer][kind 0 = split, 1 = combine][0 = earliest entry, 1 = latest exit, 2 = earliest "dependency resolved"]
+__device__ unsigned long long vteb_trace_launch[64 * 2 * 4];
+__device__ const void* vteb_trace_base[2];      // first layer's k_cache / output
+__device__ long long vteb_trace_stride[2];      // bytes between layers
+__device__ __forceinline__ void vteb_trace_launch_event(int kind, const void* p, int slot, bool is_max) {
+    const long long layer = ((const char*)p - (const char*)vteb_trace_base[kind]) / vteb_trace_stride[kind];
+    if (layer < 0 || layer >= 64) return;
+    unsigned long long* dst = &vteb_trace_launch[(layer * 2 + kind) * 4 + slot];
+    if (is_max) atomicMax(dst, vteb_global_ns()); else atomicMin(dst, vteb_global_ns());
+}
+#define VTEB_TRACE_LAUNCH(kind_, ptr_, slot_, is_max_) \
+    do { if ((threadIdx.x & 31) == 0) vteb_trace_launch_event(kind_, ptr_, slot_, is_max_); } while (0)
 #define VTEB_TRACE_EVENT(warp_, tile_, slot_) \
     do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile_) < 64) \
         vteb_trace_buf[((warp_) * 64 + (tile_)) * 4 + (slot_)] = clock64(); } while (0)
 #else
 #define VTEB_TRACE_EVENT(warp_, tile_, slot_) do {} while (0)
+#define VTEB_TRACE_CTA(slot_) do {} while (0)
+#define VTEB_TRACE_LAUNCH(kind_, ptr_, slot_, is_max_) do {} while (0)
 #endif
 
 #ifndef SPLIT_KV_CHUNK_SIZE
@@ -272,12 +294,14 @@ extern "C" __global__ void flash_attention_split_kv_reduce_f32_kernel(
 }
 
 // ---------------------------------------------------------------------------
-// Fast combine: grid (B * Hq * dsplit, 1, 1), block 256, dynamic shared memory
-// max_chunks * 4 + 8 * dchunk * 4 bytes, where dchunk = head_dim / dsplit.
-// Warp w accumulates splits w, w+8, ... for the CTA's slice of head_dim, the
-// eight warp sums are added through shared memory.  Neutral splits are
-// skipped.  The CTA with index 0 also clears the work-queue ticket so the next
-// split launch starts from zero.
+// Fast combine: grid (B * Hq * D/32, 1, 1), block 256, dynamic shared memory
+// max_chunks * 4 bytes.  One CTA merges the splits of one (sequence, query
+// head) for 32 output columns.  Thread (r = tid / 8, q = tid % 8) owns the
+// float4 columns 4q..4q+3 of splits r, r+32, r+64, ...; every global load of a
+// pass (m, l and up to eight partial_o rows per thread) is issued before any of
+// them is used, so a CTA pays one L2 round trip, not one per split.  Neutral
+// splits get weight 0 and their partial_o is never used.  CTA 0 also clears the
+// work-queue ticket so the next split launch starts from zero.
 // ---------------------------------------------------------------------------
 template <typename OutT>
 __device__ __forceinline__ void fast_combine_body(
@@ -285,68 +309,91 @@ __device__ __forceinline__ void fast_combine_body(
     const float* __restrict__ partial_o, OutT* __restrict__ output,
     int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
-    extern __shared__ float csh[];
-    float* weight_sh = csh;                  // [max_chunks]
-    float* acc_sh = csh + max_chunks;        // [8][dchunk]
-    __shared__ float scratch[32];
+    extern __shared__ float weight_sh[];           // [max_chunks]
+    __shared__ float red_max[8], red_sum[8];
+    __shared__ float4 acc_sh[8][8];                // [warp][q]
+    VTEB_TRACE_LAUNCH(1, output, 0, false);
     grid_launch_dependents();
     grid_dependency_wait();
+    VTEB_TRACE_LAUNCH(1, output, 2, false);
     if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
 
-    const int dchunk = head_dim / dsplit;
-    const int bh = blockIdx.x / dsplit, dpart = blockIdx.x % dsplit;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int bh = blockIdx.x / dsplit, dpart = blockIdx.x - bh * dsplit;
     const long long base = (long long)bh * max_chunks;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = tid >> 3, q = tid & 7;
+    const float* o_base = partial_o + base * head_dim + dpart * 32 + q * 4;
 
-    float mx = kNeutralM;
-    for (int c = threadIdx.x; c < max_chunks; c += blockDim.x) mx = fmaxf(mx, partial_m[base + c]);
-    const float M = block_reduce(mx, true, scratch);
-    float lsum = 0.f;
-    for (int c = threadIdx.x; c < max_chunks; c += blockDim.x) {
-        const float mc = partial_m[base + c];
-        const float w = (mc <= -1e29f) ? 0.f : __expf(mc - M);
-        weight_sh[c] = w;
-        lsum += partial_l[base + c] * w;
-    }
-    const float L = fmaxf(block_reduce(lsum, false, scratch), 1e-20f);
-
-    // dchunk is 32, 64, 128 or 256: each lane owns dchunk / 32 consecutive floats.
-    const int epl = dchunk >> 5;
-    float acc[8];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float M = kNeutralM, lsum = 0.f;
+    // max_chunks <= 256 takes one pass; longer split lists are folded pass by pass
+    // with the usual running-maximum rescale.
+    for (int c0 = 0; c0 < max_chunks; c0 += 256) {
+        const int cm = c0 + tid;
+        const float my_m = (cm < max_chunks) ? partial_m[base + cm] : kNeutralM;
+        const float my_l = (cm < max_chunks) ? partial_l[base + cm] : 0.f;
+        float4 o[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    const float* op = partial_o + base * head_dim + dpart * dchunk + lane * epl;
-    for (int c = warp; c < max_chunks; c += 8) {
-        const float w = weight_sh[c];
-        if (w == 0.f) continue;
-        const float* row = op + (long long)c * head_dim;
-        if (epl == 4) {
-            const float4 x = *reinterpret_cast<const float4*>(row);
-            acc[0] = fmaf(x.x, w, acc[0]); acc[1] = fmaf(x.y, w, acc[1]);
-            acc[2] = fmaf(x.z, w, acc[2]); acc[3] = fmaf(x.w, w, acc[3]);
-        } else if (epl == 8) {
-            const float4 x = *reinterpret_cast<const float4*>(row);
-            const float4 y = *reinterpret_cast<const float4*>(row + 4);
-            acc[0] = fmaf(x.x, w, acc[0]); acc[1] = fmaf(x.y, w, acc[1]);
-            acc[2] = fmaf(x.z, w, acc[2]); acc[3] = fmaf(x.w, w, acc[3]);
-            acc[4] = fmaf(y.x, w, acc[4]); acc[5] = fmaf(y.y, w, acc[5]);
-            acc[6] = fmaf(y.z, w, acc[6]); acc[7] = fmaf(y.w, w, acc[7]);
-        } else if (epl == 2) {
-            const float2 x = *reinterpret_cast<const float2*>(row);
-            acc[0] = fmaf(x.x, w, acc[0]); acc[1] = fmaf(x.y, w, acc[1]);
-        } else {
-            acc[0] = fmaf(row[0], w, acc[0]);
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + r + 32 * k;
+            o[k] = (c < max_chunks) ? *reinterpret_cast<const float4*>(o_base + (long long)c * head_dim)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        // ---- maximum of this pass
+        float mx = my_m;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        __syncthreads();                            // previous pass is done with red_* and weight_sh
+        if (lane == 0) red_max[warp] = mx;
+        __syncthreads();
+        float pass_max = red_max[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) pass_max = fmaxf(pass_max, red_max[w]);
+        const float M_new = fmaxf(M, pass_max);
+        const float rescale = __expf(M - M_new);    // 1 on the first pass (both neutral) or exp(-big) = 0
+        M = M_new;
+        // ---- weights and the sum of l
+        const float wgt = (my_m <= -1e29f) ? 0.f : __expf(my_m - M);
+        if (cm < max_chunks) weight_sh[cm - c0] = wgt;
+        float ls = my_l * wgt;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, off);
+        if (lane == 0) red_sum[warp] = ls;
+        __syncthreads();
+        float pass_l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) pass_l += red_sum[w];
+        lsum = lsum * rescale + pass_l;
+        acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + r + 32 * k;
+            if (c < max_chunks) {
+                const float w = weight_sh[c - c0];
+                if (w != 0.f) {
+                    acc.x = fmaf(o[k].x, w, acc.x); acc.y = fmaf(o[k].y, w, acc.y);
+                    acc.z = fmaf(o[k].z, w, acc.z); acc.w = fmaf(o[k].w, w, acc.w);
+                }
+            }
         }
     }
-    for (int i = 0; i < epl; ++i) acc_sh[warp * dchunk + lane * epl + i] = acc[i];
+    // ---- sum over the 32 row groups: lanes with equal q inside a warp, then the 8 warps
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+    }
+    if (lane < 8) acc_sh[warp][lane] = acc;
     __syncthreads();
-    const float inv = 1.f / L;
-    for (int d = threadIdx.x; d < dchunk; d += blockDim.x) {
+    if (tid < 32) {
+        const float* flat = reinterpret_cast<const float*>(acc_sh);
         float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) s += acc_sh[w * dchunk + d];
-        output[(long long)bh * head_dim + dpart * dchunk + d] = to_out<OutT>(s * inv);
+        for (int w = 0; w < 8; ++w) s += flat[w * 32 + tid];
+        const float L = fmaxf(lsum, 1e-20f);
+        output[(long long)bh * head_dim + dpart * 32 + tid] = to_out<OutT>(s / L);
     }
+    VTEB_TRACE_LAUNCH(1, output, 1, true);
 }
 
 extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f16_kernel(

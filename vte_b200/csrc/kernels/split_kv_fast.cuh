@@ -18,8 +18,9 @@
 // Consumer warp w: KV head (w % hg) of the group, every wph-th 16-position
 // block.  Per block: S = Q K^T with mma.sync m16n8k16 (Q rows are the query
 // heads of the KV head, K fragments via ldmatrix), online softmax in the log2
-// domain on the accumulator fragment, P split into an fp16 high and low part,
-// O += P V with V fragments via ldmatrix.trans.  At the end of an item the
+// domain on the accumulator fragment, P split into an fp16 high and low part
+// (high part in rows 0..7 of the A operand, low part in rows 8..15, so one mma
+// multiplies both), O += P V with V fragments via ldmatrix.trans.  At the end of an item the
 // warps of a KV head exchange (m, l, o) through shared memory and the merged
 // state is stored to partial_m / partial_l / partial_o.
 //
@@ -123,6 +124,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     const int nstages = plan.nstages;
 
     if (threadIdx.x == 0) {
+        VTEB_TRACE_CTA(0);
+        VTEB_TRACE_LAUNCH(0, a.k_cache, 0, false);
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(full0 + 8 * s, 65);        // 64 asynchronous-copy arrivals + the header writer
             mbar_init(empty0 + 8 * s, plan.active_warps);
@@ -293,6 +296,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
     grid_dependency_wait();
+    if (warp == 0) VTEB_TRACE_LAUNCH(0, a.k_cache, 2, false);
     if (blockIdx.x < total_items) {
         const int items_per_seq = plan.n_hgroups * a.max_chunks;
         const int rank = blockIdx.x / items_per_seq;
@@ -309,9 +313,10 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
         full_parity ^= (1u << stage);
         VTEB_TRACE_EVENT(warp, trace_tile, 1);
+        if (warp == 0 && trace_tile == 0) VTEB_TRACE_CTA(1);
         const TileHeader* hd = headers + stage;
         const int flags = hd->flags;
-        if (flags & kTileStop) break;
+        if (flags & kTileStop) { if (warp == 0) { VTEB_TRACE_CTA(3); VTEB_TRACE_LAUNCH(0, a.k_cache, 1, true); } break; }
         // Copy what is needed later: the loader may rewrite the header once every
         // consumer warp has released the stage.
         const int item_b = hd->b, item_hgroup = hd->hgroup, item_c = hd->c;
@@ -409,14 +414,11 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 #pragma unroll
                 for (int i = 0; i < VC; ++i) {
                     const int n = 2 * (ch * VC + i);
-                    mma_rows0to7(o_acc[n][0], o_acc[n][1], ph[0], ph[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
-                    mma_rows0to7(o_acc[n + 1][0], o_acc[n + 1][1], ph[0], ph[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
-                }
-#pragma unroll
-                for (int i = 0; i < VC; ++i) {
-                    const int n = 2 * (ch * VC + i);
-                    mma_rows0to7(o_acc[n][0], o_acc[n][1], pl[0], pl[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
-                    mma_rows0to7(o_acc[n + 1][0], o_acc[n + 1][1], pl[0], pl[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
+                    float e0, e1, f0, f1;
+                    mma_hi_lo(o_acc[n][0], o_acc[n][1], e0, e1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
+                    mma_hi_lo(o_acc[n + 1][0], o_acc[n + 1][1], f0, f1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
+                    // rows 8..15 of A carried P_lo; their product belongs to this thread's row too
+                    o_acc[n][0] += e0; o_acc[n][1] += e1; o_acc[n + 1][0] += f0; o_acc[n + 1][1] += f1;
                 }
             }
         }
@@ -425,6 +427,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * stage);
         VTEB_TRACE_EVENT(warp, trace_tile, 2);
+        if (warp == 0) VTEB_TRACE_CTA(2);
         ++trace_tile;
 
         if (flags & kTileLast) {

@@ -234,6 +234,18 @@ __device__ __forceinline__ void mma_rows0to7(float& d0, float& d1, uint32_t a_lo
         : "r"(a_lo), "r"(0u), "r"(a_hi), "r"(0u), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f));
 }
 
+// D(16x8) = A(16x16) * B(16x8) + C with rows 0..7 of A = (hi_lo, hi_hi) and rows
+// 8..15 of A = (lo_lo, lo_hi): one instruction multiplies both fp16 halves of a
+// split-precision operand by the same B.  d0, d1 accumulate the rows 0..7
+// product; e0, e1 return the rows 8..15 product (started from zero).
+__device__ __forceinline__ void mma_hi_lo(float& d0, float& d1, float& e0, float& e1, uint32_t hi_lo, uint32_t lo_lo,
+                                          uint32_t hi_hi, uint32_t lo_hi, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%11};"
+        : "+f"(d0), "+f"(d1), "=f"(e0), "=f"(e1)
+        : "r"(hi_lo), "r"(lo_lo), "r"(hi_hi), "r"(lo_hi), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f));
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float x, float y) {
     __half2 h = __floats2half2_rn(x, y);
     return *reinterpret_cast<uint32_t*>(&h);

@@ -503,10 +503,8 @@ int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fas
     plan->nstages = p.nstages;
     plan->smem_bytes = p.smem_bytes;
     plan->threads = vteb::kFastThreads;
-    int dsplit = 1;
-    if (head_dim >= 64 && head_dim % 64 == 0) dsplit = head_dim / 64;   // 64-wide slices
-    plan->combine_dsplit = dsplit;
-    plan->combine_smem_bytes = 4 + 8 * (dsplit ? head_dim / dsplit : head_dim) * 4;
+    plan->combine_dsplit = head_dim >= 32 ? head_dim / 32 : 1;   // one CTA per 32 output columns
+    plan->combine_smem_bytes = 4;
     return 0;
 }
 
@@ -598,7 +596,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     vteb_fast_plan hp;
     vteb_split_kv_plan(num_q_heads, num_kv_heads, head_dim, &hp);
     const int dsplit = hp.combine_dsplit;
-    const size_t csmem = (size_t)max_chunks * 4 + 8 * (size_t)(head_dim / dsplit) * 4;
+    const size_t csmem = (size_t)(max_chunks < 256 ? max_chunks : 256) * 4;
     if (out_is_f32)
         return launch_rt(vteb_split_kv_combine_f32_kernel, dim3(batch * num_q_heads * dsplit), dim3(256), csmem,
                          s, pdl, (const float*)partial_m, (const float*)partial_l, (const float*)partial_o,
