@@ -316,33 +316,46 @@ def run_ours(args, rank, world, local_rank):
     return 0
 
 
-def kernel_durations(rt, ex, n_layers, reps=3):
-    """Average duration of the split kernel (and of the combine kernel) measured
-    with CUDA events recorded on the launching stream right before and after
-    each launch, layers in their normal order, no programmatic overlap."""
+def kernel_durations(rt, ex, n_layers, reps=10):
+    """Average launch duration of the split kernel and of the combine kernel.
+    CUDA events cannot bracket one kernel inside a replayed graph, so each kernel
+    is captured into a graph of its own (every layer's launch of that kernel, in
+    layer order, plain stream serialisation) and the graph is timed with events
+    on the launching stream: duration = elapsed / (replays * layers), which
+    includes the in-graph launch gap between consecutive kernels."""
     disp = ex.dispatcher
-    evs = [(rt.event_create(), rt.event_create(), rt.event_create()) for _ in range(n_layers)]
-    split_us, combine_us = [], []
     name = "flash_attention_split_kv_partial_kernel" if disp.compat else f"vteb_split_kv_partial_d{disp.head_dim}_kernel"
-    for rep in range(reps + 1):
-        for l in range(n_layers):
-            launches = disp.build_launches(l, ex.tensor_mapping, ex.offsets.ptr, batch=ex.B)[1:]
-            a, b, c = evs[l]
-            rt.event_record(a)
-            rt.launch_kernel_recorded(*launches[0][:1], launches[0][1], launches[0][2], launches[0][3], launches[0][4])
-            rt.event_record(b)
-            rt.launch_kernel_recorded(*launches[1][:1], launches[1][1], launches[1][2], launches[1][3], launches[1][4])
-            rt.event_record(c)
+    out = {}
+    for which, key in ((0, "split_us"), (1, "combine_us")):
+        rt.stream_begin_capture()
+        try:
+            for l in range(n_layers):
+                launches = disp.build_launches(l, ex.tensor_mapping, ex.offsets.ptr, batch=ex.B)[1:]
+                fn, args, grid, block, smem = launches[which]
+                if which == 0 and not disp.compat and ex.B * disp._plan.n_hgroups * disp.max_chunks > grid[0]:
+                    # more items than CTAs: the work-queue ticket, normally cleared by the
+                    # combine launch, has to start from zero
+                    rt.memset_async(ctypes.c_void_p(disp.work_ptr), 4, 0, "attn_splitkv_work")
+                rt.launch_kernel_recorded(fn, args, grid, block, smem)
+        finally:
+            graph = rt.stream_end_capture()
+        gexec = rt.graph_instantiate(graph)
+        rt.graph_destroy(graph)
+        e0, e1 = rt.event_create(), rt.event_create()
+        for _ in range(3):
+            rt.graph_launch(gexec)
         rt.synchronize()
-        if rep == 0:
-            continue
-        for a, b, c in evs:
-            split_us.append(rt.event_elapsed_ms(a, b) * 1e3)
-            combine_us.append(rt.event_elapsed_ms(b, c) * 1e3)
-    for tup in evs:
-        for e in tup:
-            rt.event_destroy(e)
-    return {"split_name": name, "split_us": statistics.median(split_us), "combine_us": statistics.median(combine_us)}
+        rt.event_record(e0)
+        for _ in range(reps):
+            rt.graph_launch(gexec)
+        rt.event_record(e1)
+        rt.synchronize()
+        out[key] = rt.event_elapsed_ms(e0, e1) * 1e3 / (reps * n_layers)
+        rt.graph_exec_destroy(gexec)
+        rt.event_destroy(e0)
+        rt.event_destroy(e1)
+    out["split_name"] = name
+    return out
 
 
 def main():

@@ -28,6 +28,8 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_partial_d256_kernel": _FAST_PARTIAL,
     "vteb_split_kv_combine_f16_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_f32_kernel": _FAST_COMBINE,
+    "vteb_split_kv_combine_state_kernel": _FAST_COMBINE,
+    "vteb_merge_shard_states_kernel": [P, P, I, I, I],
 }
 
 # template name (what the reference passes to load_kernel_safe) -> source file

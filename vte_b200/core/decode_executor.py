@@ -31,7 +31,8 @@ class DecodeAttentionExecutor:
                  n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, output_f32: bool = True,
                  use_graph: bool = True, programmatic: Optional[bool] = None, compat: bool = False,
                  with_append: bool = False, fixed_chunk_size=None, min_chunk: Optional[int] = None,
-                 strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None):
+                 strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
+                 emit_state: bool = False, per_layer_hook=None):
         self.hip = hip
         self.metadata = dict(metadata)
         self.B = int(batch_size)
@@ -47,6 +48,8 @@ class DecodeAttentionExecutor:
         self.use_graph = bool(use_graph)
         self.programmatic = (not env_flag(ENV_NO_PDL)) if programmatic is None else bool(programmatic)
         self.with_append = bool(with_append)
+        self.emit_state = bool(emit_state)          # outputs are [B, Hq, D + 2] fp32 shard states
+        self.per_layer_hook = per_layer_hook        # called as hook(layer) after a layer's launches are recorded
         self.kv_batch_stride = self.S * self.Hkv * self.D
         if self.kv_batch_stride >= 2 ** 31:
             raise CudaSafetyError("one sequence's cache exceeds 2^31 elements: the kernel ABI's stride is an int")
@@ -56,6 +59,8 @@ class DecodeAttentionExecutor:
         self.q_bytes = self.B * self.Hq * self.D * 2
         self.kvnew_bytes = self.B * self.Hkv * self.D * 2
         self.out_bytes = self.B * self.Hq * self.D * out_elem
+        if self.emit_state:
+            self.out_bytes = self.B * self.Hq * (self.D + 2) * 4
 
         self._owns_allocator = allocator is None
         if allocator is None:
@@ -68,7 +73,7 @@ class DecodeAttentionExecutor:
         self.dispatcher = SplitKVAttentionDispatcher(
             hip, codegen, self.metadata, allocator=allocator, context_length=self.S, batch_size=self.B,
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
-            output_f32=self.output_f32, strict_empty_splits=strict_empty_splits)
+            output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state)
 
         A = allocator.allocate
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
@@ -148,6 +153,8 @@ class DecodeAttentionExecutor:
             for fn, args, grid, block, smem in launches:
                 self.hip.launch_kernel_recorded(fn, args, grid, block, smem)
                 n += 1
+            if self.per_layer_hook is not None:
+                n += int(self.per_layer_hook(l) or 0)
         return n
 
     def build_decode_graph(self):
@@ -209,9 +216,9 @@ class DecodeAttentionExecutor:
         self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), nbytes, "attention output")
         self.hip.stream_synchronize()
         self.dispatcher_check()
-        dt = np.float32 if self.output_f32 else np.float16
+        dt = np.float32 if (self.output_f32 or self.emit_state) else np.float16
         flat = np.frombuffer((ctypes.c_char * nbytes).from_address(self._stage_out.value), dtype=dt)
-        return flat.reshape(self.L, self.B, self.Hq, self.D).copy()
+        return flat.reshape(self.L, self.B, self.Hq, self.D + 2 if self.emit_state else self.D).copy()
 
     execute_decode = execute_decode_batch
 

@@ -1,0 +1,98 @@
+"""Decode attention for one very long sequence whose KV range is split across GPUs.
+
+Rank r of n holds positions [r * S / n, (r + 1) * S / n) of every layer's cache
+(its local kv offset is S / n - 1).  Per layer each rank runs the split kernel
+over its own range, reduces its splits to one unnormalised state per query head
+(o[D], m, l: 6,240 bytes for 12 heads of 128), all ranks all-gather the states
+with NCCL over NVLink, and every rank applies the log-sum-exp merge over the
+shard axis.  No remote K/V is ever read.  The reference has no multi-GPU path;
+the merge is the arithmetic of its reduce kernel
+(flash_attention_split_kv_reduce.hip.template:24-66) run over shards.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import numpy as np
+
+from ..bridge.errors import CudaSafetyError
+from ..bridge.memory import MemoryRegion
+from .decode_executor import DecodeAttentionExecutor
+
+
+def kv_range_of_rank(total: int, rank: int, world: int) -> tuple[int, int]:
+    """[start, end) of the positions rank `rank` owns; ranges are contiguous, cover
+    0..total and differ in length by at most one."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside 0..{world - 1}")
+    return rank * total // world, (rank + 1) * total // world
+
+
+def sequences_of_rank(batch: int, rank: int, world: int) -> tuple[int, int]:
+    """[first, last) sequence indices of rank `rank` when a batch is sharded by
+    sequence (contiguous blocks, no collective)."""
+    return kv_range_of_rank(batch, rank, world)
+
+
+class KVRangeShardedDecode:
+    def __init__(self, hip, codegen, metadata: dict, shard_context_length: int, n_layers: int, comm, *,
+                 n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, programmatic: Optional[bool] = None):
+        self.hip, self.comm = hip, comm
+        self.world = comm.world if comm is not None else 1
+        self.L = int(n_layers)
+        self.ex = DecodeAttentionExecutor(hip, codegen, metadata, 1, shard_context_length, n_layers,
+                                          n_kv_buffers=n_kv_buffers, num_splits=num_splits, emit_state=True,
+                                          programmatic=programmatic, per_layer_hook=self._after_layer)
+        ex = self.ex
+        self.rows = ex.B * ex.Hq
+        self.state_floats = self.rows * (ex.D + 2)
+        A = ex.allocator.allocate
+        self.gathered = A(self.L * self.world * self.state_floats * 4, "shard_states.gathered", MemoryRegion.ACTIVATIONS)
+        self.merged = A(self.L * self.rows * ex.D * 4, "attention.output.merged", MemoryRegion.ACTIVATIONS)
+        arch = hip.get_gpu_architecture()
+        _, self._merge_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_kernel')
+        self._stage_merged = hip.host_alloc(self.L * self.rows * ex.D * 4)
+
+    def _after_layer(self, l: int) -> int:
+        """Recorded right after layer l's split + state-combine launches: all-gather, merge."""
+        ex = self.ex
+        state_ptr = ex.out_all.ptr + l * ex.out_bytes
+        gathered_ptr = self.gathered.ptr + l * self.world * self.state_floats * 4
+        if self.world > 1:
+            self.comm.all_gather_f32(state_ptr, gathered_ptr, self.state_floats)
+        else:
+            gathered_ptr = state_ptr               # one shard: its own state is the gathered list
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        args = [vp(gathered_ptr), vp(self.merged.ptr + l * self.rows * ex.D * 4), ci(self.world), ci(self.rows), ci(ex.D)]
+        pdl = self.hip.programmatic_launch
+        self.hip.programmatic_launch = False        # ordinary edge after a collective
+        try:
+            self.hip.launch_kernel_recorded(self._merge_fn, args, (self.rows, 1, 1), (ex.D, 1, 1), 0)
+        finally:
+            self.hip.programmatic_launch = pdl
+        return 2 if self.world > 1 else 1
+
+    def execute_decode(self, local_kv_offset: int) -> np.ndarray:
+        """One decode step; returns the merged attention output [L, Hq, D] fp32
+        (identical on every rank)."""
+        ex = self.ex
+        ex.build_decode_graph()
+        ex._update_staging_buffers(np.array([local_kv_offset], dtype=np.int32))
+        ex.launch_step()
+        nbytes = self.L * self.rows * ex.D * 4
+        self.hip.memcpy_d2h_async(self._stage_merged, ctypes.c_void_p(self.merged.ptr), nbytes, "attention output merged")
+        self.hip.stream_synchronize()
+        ex.dispatcher_check()
+        flat = np.frombuffer((ctypes.c_char * nbytes).from_address(self._stage_merged.value), dtype=np.float32)
+        return flat.reshape(self.L, ex.Hq, ex.D).copy()
+
+    def launch_step(self):
+        self.ex.build_decode_graph()
+        self.ex.launch_step()
+
+    def cleanup(self):
+        if self._stage_merged is not None and self._stage_merged.value:
+            self.hip.host_free(self._stage_merged)
+            self._stage_merged = None
+        self.ex.cleanup()

@@ -61,7 +61,7 @@ class SplitKVAttentionDispatcher:
     def __init__(self, hip, codegen, metadata: dict, allocator=None, context_length: int = 4096,
                  batch_size: int = 1, *, num_splits: int | None = None, fixed_chunk_size=None,
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
-                 strict_empty_splits: bool = False):
+                 strict_empty_splits: bool = False, emit_state: bool = False):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -70,6 +70,9 @@ class SplitKVAttentionDispatcher:
         self.context_length = int(context_length)
         self.output_f32 = bool(output_f32)
         self.strict_empty_splits = bool(strict_empty_splits)
+        # emit_state: the reduce launch writes one unnormalised (o[D], m, l) row per query head
+        # instead of the attention output; used when the KV range is sharded across GPUs
+        self.emit_state = bool(emit_state)
         self.compat = bool(os.environ.get(ENV_COMPAT_KERNELS)) if compat is None else bool(compat)
 
         self.num_q_heads = int(self.metadata.get('attention.head_count', 12))
@@ -81,6 +84,8 @@ class SplitKVAttentionDispatcher:
         self._plan = None
         if hip is not None and hasattr(hip, 'split_kv_plan'):
             self._plan = hip.split_kv_plan(self.num_q_heads, self.num_kv_heads, self.head_dim)
+        if self.emit_state and (self.compat or self._plan is None or not self._plan.ok):
+            raise CudaSafetyError("emit_state needs the fast kernels (group <= 8, head_dim 64/128/256)")
         if not self.compat and (self._plan is None or not self._plan.ok):
             # geometry outside the fast kernel (group > 8, unusual head_dim): reference-geometry kernels
             self.compat = True
@@ -153,6 +158,7 @@ class SplitKVAttentionDispatcher:
                 self._kernel_cache['partial'] = load('decode_attention', f'vteb_split_kv_partial_d{self.head_dim}_kernel')
                 self._kernel_cache['reduce'] = load(
                     'decode_attention',
+                    'vteb_split_kv_combine_state_kernel' if self.emit_state else
                     'vteb_split_kv_combine_f32_kernel' if self.output_f32 else 'vteb_split_kv_combine_f16_kernel')
 
             # One scratch set shared by every layer: layers run strictly one after

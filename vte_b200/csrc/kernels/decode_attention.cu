@@ -303,7 +303,7 @@ extern "C" __global__ void flash_attention_split_kv_reduce_f32_kernel(
 // splits get weight 0 and their partial_o is never used.  CTA 0 also clears the
 // work-queue ticket so the next split launch starts from zero.
 // ---------------------------------------------------------------------------
-template <typename OutT>
+template <typename OutT, bool kEmitState = false>
 __device__ __forceinline__ void fast_combine_body(
     const float* __restrict__ partial_m, const float* __restrict__ partial_l,
     const float* __restrict__ partial_o, OutT* __restrict__ output,
@@ -390,8 +390,15 @@ __device__ __forceinline__ void fast_combine_body(
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) s += flat[w * 32 + tid];
-        const float L = fmaxf(lsum, 1e-20f);
-        output[(long long)bh * head_dim + dpart * 32 + tid] = to_out<OutT>(s / L);
+        if constexpr (kEmitState) {
+            // unnormalised state of this shard: o[D], then m (natural-log units), then l
+            float* st = reinterpret_cast<float*>(output) + (long long)bh * (head_dim + 2);
+            st[dpart * 32 + tid] = s;
+            if (dpart == 0 && tid == 0) { st[head_dim] = M; st[head_dim + 1] = lsum; }
+        } else {
+            const float L = fmaxf(lsum, 1e-20f);
+            output[(long long)bh * head_dim + dpart * 32 + tid] = to_out<OutT>(s / L);
+        }
     }
     VTEB_TRACE_LAUNCH(1, output, 1, true);
 }
@@ -410,6 +417,44 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f32_kern
     int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
     fast_combine_body<float>(partial_m, partial_l, partial_o, output, num_q_heads, head_dim, max_chunks, dsplit, ticket);
+}
+
+// ---------------------------------------------------------------------------
+// KV-range sharding across GPUs (one very long sequence): every GPU reduces its
+// own splits to ONE unnormalised state per query head, laid out as
+// [B * Hq][D + 2] floats = o[D], m, l (6,240 bytes for 12 heads of 128), the
+// states are all-gathered, and vteb_merge_shard_states_kernel applies the same
+// log-sum-exp merge over the shard axis.  No counterpart in the reference, which
+// is single-GPU; the arithmetic is that of
+// flash_attention_split_kv_reduce.hip.template:24-66.
+// ---------------------------------------------------------------------------
+extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_state_kernel(
+    const float* __restrict__ partial_m, const float* __restrict__ partial_l,
+    const float* __restrict__ partial_o, float* __restrict__ state,
+    int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
+{
+    fast_combine_body<float, true>(partial_m, partial_l, partial_o, state, num_q_heads, head_dim, max_chunks, dsplit, ticket);
+}
+
+// gathered: [n_shards][rows][D + 2]; out: [rows][D] fp32.  grid (rows, 1, 1), block (D, 1, 1).
+extern "C" __global__ void vteb_merge_shard_states_kernel(
+    const float* __restrict__ gathered, float* __restrict__ out, int n_shards, int rows, int head_dim)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int row = blockIdx.x, pitch = head_dim + 2;
+    float M = kNeutralM;
+    for (int r = 0; r < n_shards; ++r) M = fmaxf(M, gathered[((long long)r * rows + row) * pitch + head_dim]);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.f, L = 0.f;
+        for (int r = 0; r < n_shards; ++r) {
+            const float* st = gathered + ((long long)r * rows + row) * pitch;
+            const float m = st[head_dim];
+            const float w = (m <= -1e29f) ? 0.f : __expf(m - M);
+            if (w != 0.f) { acc = fmaf(st[d], w, acc); L = fmaf(st[head_dim + 1], w, L); }
+        }
+        out[(long long)row * head_dim + d] = acc / fmaxf(L, 1e-20f);
+    }
 }
 
 #include "split_kv_fast.cuh"
