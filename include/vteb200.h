@@ -165,6 +165,31 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                          float scale, long long kv_batch_stride, int max_chunks,
                          int min_chunk, unsigned flags, int n_ctas, void* stream);
 
+/* Same computation as vteb_split_kv_decode for callers that cannot allocate
+ * device memory: code running inside a CUDA stream capture, a host callback or
+ * a latency-critical serving loop where cudaMalloc (which may synchronise the
+ * device and is forbidden during capture) is off the table, or a plugin host
+ * that hands this library tensors but no allocator.  It has no counterpart in
+ * the reference.  The split partials and the work-queue words live in a
+ * file-scope device array inside the library (VTEB_NOALLOC_SCRATCH_BYTES, held
+ * by every GPU that loads the library until the process exits); the caller
+ * passes only inputs and the output.
+ *   - Limit: batch * Hq * max_chunks * (D + 2) * 4 + 768 bytes must fit the
+ *     array; larger requests return VTEB_ERR_TOO_LARGE and launch nothing.
+ *   - The first call on a device resolves the array's device address
+ *     (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make
+ *     that first call before any stream capture begins.
+ *   - Every call uses the same array and finds the previous call's contents in
+ *     it: the entry point clears the two words that must start at zero, and two
+ *     calls that overlap on the GPU (different streams, no ordering) race.
+ *   - It calls no cudaMalloc, cudaFree or other allocating routine. */
+#define VTEB_NOALLOC_SCRATCH_BYTES (16u << 20)
+int vteb_split_kv_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                 const int* kv_offsets, void* output, int out_is_f32,
+                                 int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                                 float scale, long long kv_batch_stride, int max_chunks,
+                                 int min_chunk, unsigned flags, int n_ctas, void* stream);
+
 /* Writes the current token's K/V rows at position kv_offsets[b]
  * (kv_cache_append.hip.template:13-39; launch built at split_kv_attention.py:186-194). */
 int vteb_kv_cache_append(const void* k, const void* v, void* k_cache, void* v_cache,

@@ -117,6 +117,7 @@ def _declare(lib):
         "vteb_nccl_comm_destroy": (i, [vp]),
         "vteb_split_kv_plan": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
         "vteb_split_kv_decode": (i, [vp, vp, vp, vp, vp, i, vp, vp, vp, vp, i, i, i, i, f, ll, i, i, u, i, vp]),
+        "vteb_split_kv_decode_noalloc": (i, [vp, vp, vp, vp, vp, i, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_kv_cache_append": (i, [vp, vp, vp, vp, vp, i, i, i, ll, vp]),
         "vteb_check_status": (i, [vp, vp]),
         "vteb_fill_normal_f16": (i, [vp, sz, ull, f, f, f, vp]),
@@ -624,6 +625,24 @@ class CudaRuntime:
         if err < 0:
             raise CudaSafetyError(f"vteb_split_kv_decode refused the call ({err}): {self._last_error()}")
         self._check_error(err, "vteb_split_kv_decode")
+
+    def split_kv_decode_noalloc(self, q, k_cache, v_cache, kv_offsets, output, out_is_f32: bool, batch: int,
+                                num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float, kv_batch_stride: int,
+                                max_chunks: int, min_chunk: int = 0, flags: int = 0, n_ctas: int = 0) -> None:
+        """One layer's split + combine with the library's built-in scratch: for
+        callers that must not allocate (inside a stream capture, a plugin without
+        an allocator).  Requests beyond the 16 MiB array raise CudaSafetyError.
+        The first call on a device does one-time set-up, so make it before any
+        capture; calls share the scratch and must not overlap on the GPU."""
+        self._require_init()
+        v = lambda p: ctypes.c_void_p(_ptr_value(p))
+        err = self._lib.vteb_split_kv_decode_noalloc(v(q), v(k_cache), v(v_cache), v(kv_offsets), v(output),
+                                                     int(bool(out_is_f32)), batch, num_q_heads, num_kv_heads, head_dim,
+                                                     float(scale), int(kv_batch_stride), max_chunks, min_chunk, flags,
+                                                     n_ctas, self._stream)
+        if err < 0:
+            raise CudaSafetyError(f"vteb_split_kv_decode_noalloc refused the call ({err}): {self._last_error()}")
+        self._check_error(err, "vteb_split_kv_decode_noalloc")
 
     def kv_cache_append(self, k, v, k_cache, v_cache, kv_offsets, batch: int, num_kv_heads: int, head_dim: int,
                         kv_batch_stride: int) -> None:

@@ -606,6 +606,51 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                      (__half*)output, num_q_heads, head_dim, max_chunks, dsplit, work);
 }
 
+// ---- the entry point that allocates nothing ---------------------------------
+// Scratch for callers that may not allocate: one array per GPU that loads this
+// library.  In host code `g_noalloc_scratch` is only a handle for the runtime's
+// symbol lookup, never a device address; the address is resolved once per device.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[VTEB_NOALLOC_SCRATCH_BYTES];
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+int vteb_split_kv_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const int* kv_offsets,
+                                 void* output, int out_is_f32, int batch, int num_q_heads, int num_kv_heads,
+                                 int head_dim, float scale, long long kv_batch_stride, int max_chunks,
+                                 int min_chunk, unsigned flags, int n_ctas, void* stream) {
+    REQUIRE_INIT();
+    if (batch <= 0 || num_q_heads <= 0 || max_chunks <= 0 || head_dim <= 0)
+        return fail(VTEB_ERR_INVALID_ARGUMENT, "non-positive dimension");
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    const size_t stats = up((size_t)batch * num_q_heads * max_chunks * 4);
+    const size_t obytes = up((size_t)batch * num_q_heads * max_chunks * head_dim * 4);
+    const size_t need = 256 + 2 * stats + obytes;
+    if (need > VTEB_NOALLOC_SCRATCH_BYTES)
+        return fail(VTEB_ERR_TOO_LARGE,
+                    "vteb_split_kv_decode_noalloc: batch %d x %d heads x %d splits x head_dim %d needs %zu bytes of scratch, "
+                    "the built-in array holds %u; use fewer splits or vteb_split_kv_decode with caller scratch",
+                    batch, num_q_heads, max_chunks, head_dim, need, (unsigned)VTEB_NOALLOC_SCRATCH_BYTES);
+    if (g_device < 0 || g_device >= 64) return fail(VTEB_ERR_UNSUPPORTED, "device index %d not supported", g_device);
+    if (g_noalloc_ptr[g_device] == nullptr) {
+        // one-time set-up on this device (which vteb_init made current)
+        void* p = nullptr;
+        int rc = check_rt(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
+        if (rc) return rc;
+        if (p == nullptr) return fail(VTEB_ERR_DRIVER_ENTRY, "scratch symbol resolved to a null address");
+        g_noalloc_ptr[g_device] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = g_noalloc_ptr[g_device];
+    int* work = reinterpret_cast<int*>(base);
+    float* pm = reinterpret_cast<float*>(base + 256);
+    float* pl = reinterpret_cast<float*>(base + 256 + stats);
+    float* po = reinterpret_cast<float*>(base + 256 + 2 * stats);
+    // the work-queue ticket and the status word must start at zero
+    int rc = check_rt(cudaMemsetAsync(work, 0, 16, (cudaStream_t)stream), "scratch clear");
+    if (rc) return rc;
+    return vteb_split_kv_decode(q, k_cache, v_cache, kv_offsets, output, out_is_f32, pm, pl, po, work, batch,
+                                num_q_heads, num_kv_heads, head_dim, scale, kv_batch_stride, max_chunks, min_chunk,
+                                flags, n_ctas, stream);
+}
+
 int vteb_kv_cache_append(const void* k, const void* v, void* k_cache, void* v_cache, const int* kv_offsets,
                          int batch, int num_kv_heads, int head_dim, long long kv_batch_stride, void* stream) {
     REQUIRE_INIT();
