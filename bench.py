@@ -142,7 +142,8 @@ def run_reference(args, rank, world):
     cfg = CONFIGS[args.workload]
     lengths = draw_context_lengths(cfg)
     n_layers = args.layers or cfg.layers
-    sample_layers = min(n_layers, args.cpu_layers)
+    # one layer per host thread: numpy's einsum is single-threaded, layers are independent
+    sample_layers = min(n_layers, max(args.cpu_layers, os.cpu_count() or 1))
     layers = [make_layer_inputs(cfg, l) for l in range(sample_layers)]
     threads = max(1, min(os.cpu_count() or 1, sample_layers))
     bytes_step = algorithmic_bytes(cfg, lengths) * sample_layers
@@ -193,7 +194,8 @@ def run_ours(args, rank, world, local_rank):
         n_kv = min(n_kv, args.kv_buffers)
     ex = DecodeAttentionExecutor(rt, CodegenEngine(), metadata(cfg), cfg.batch, cfg.max_seq, n_layers,
                                  n_kv_buffers=n_kv, num_splits=args.splits or None, output_f32=True,
-                                 programmatic=not args.no_pdl, compat=args.compat)
+                                 programmatic=not args.no_pdl, compat=args.compat,
+                                 prefetch_next_layer=not args.no_prefetch)
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
@@ -275,7 +277,8 @@ def run_ours(args, rank, world, local_rank):
             "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
             "config": config_json(cfg, args.workload, lengths, n_layers, n_kv, ex.dispatcher.max_chunks, world,
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
-                                   "programmatic_dependent_launch": not args.no_pdl, "kernels": "compat" if args.compat else "fast"}),
+                                   "programmatic_dependent_launch": not args.no_pdl,
+                                   "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1, "kernels": "compat" if args.compat else "fast"}),
             "us_per_layer_token": step_s * 1e6 / n_layers / cfg.batch,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
             "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
@@ -370,6 +373,7 @@ def main():
     ap.add_argument("--splits", type=int, default=0, help="split count (0 = dispatcher's choice)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")
     ap.add_argument("--device-fill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")

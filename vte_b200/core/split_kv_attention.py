@@ -61,7 +61,7 @@ class SplitKVAttentionDispatcher:
     def __init__(self, hip, codegen, metadata: dict, allocator=None, context_length: int = 4096,
                  batch_size: int = 1, *, num_splits: int | None = None, fixed_chunk_size=None,
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
-                 strict_empty_splits: bool = False, emit_state: bool = False):
+                 strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -73,6 +73,8 @@ class SplitKVAttentionDispatcher:
         # emit_state: the reduce launch writes one unnormalised (o[D], m, l) row per query head
         # instead of the attention output; used when the KV range is sharded across GPUs
         self.emit_state = bool(emit_state)
+        # hand the split kernel the next layer's caches so its loaders can pull them into L2
+        self.prefetch_next_layer = bool(prefetch_next_layer)
         self.compat = bool(os.environ.get(ENV_COMPAT_KERNELS)) if compat is None else bool(compat)
 
         self.num_q_heads = int(self.metadata.get('attention.head_count', 12))
@@ -245,8 +247,15 @@ class SplitKVAttentionDispatcher:
         items = batch * plan.n_hgroups * C
         n_ctas = max(1, min(items, self.num_sms))
         flags = FLAG_WRITE_EMPTY_O if self.strict_empty_splits else 0
+        next_k = next_v = 0
+        if self.prefetch_next_layer:
+            next_k, next_v = self._resolve_kv_cache_ptrs(layer_idx + 1, {k: v for k, v in tensor_mapping.items()
+                                                                         if k != 'KV Cache Pool'})
+            if not (next_k and next_v) or next_k % 16 or next_v % 16:
+                next_k = next_v = 0
         partial_args = reference_partial_args + [
-            ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4)]
+            ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4),
+            vp(next_k), vp(next_v)]
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
         dsplit = plan.combine_dsplit
         combine_args = reduce_args + [ci(dsplit), vp(self._work.ptr)]

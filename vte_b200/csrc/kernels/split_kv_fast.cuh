@@ -35,6 +35,7 @@ struct FastArgs {
     int num_q_heads, num_kv_heads; float scale;
     const int* kv_offsets; long long kv_batch_stride; int max_chunks;
     int batch, min_chunk, flags; const int* seq_order; int* ticket; int* status;
+    const __half* next_k_cache; const __half* next_v_cache;   // optional: the next layer's caches, for L2 prefetch
 };
 
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
@@ -84,6 +85,20 @@ __device__ __forceinline__ void copy_rows_async(const unsigned char* src, const 
     }
 }
 
+// When a CTA owns exactly one item (one sequence, splits <= CTAs) and the
+// dispatcher passed the next layer's cache, a loader warp that has issued its last
+// copy asks L2 to fetch the byte range the same CTA will stream in the next
+// layer's launch.  HBM then stays busy while this launch drains its tail and the
+// combine runs, and the next launch starts from L2.  Every byte is still read
+// from HBM once per step.  Requests are 8 KB each, spread over the lanes.
+__device__ __forceinline__ void prefetch_range_l2(const unsigned char* base, long long bytes, int lane) {
+    constexpr long long kPiece = 8192;
+    for (long long off = (long long)lane * kPiece; off < bytes; off += 32 * kPiece) {
+        const unsigned n = (unsigned)((bytes - off < kPiece) ? (bytes - off) : kPiece) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
+    }
+}
+
 struct ItemGeometry {
     int b, hgroup, c, start, end;   // end <= start: empty item
 };
@@ -123,6 +138,13 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nstages = plan.nstages;
 
+    // The first item's geometry needs one global load (the sequence's kv offset): start it
+    // before the barrier set-up so its latency is hidden.
+    const int total_items = a.batch * plan.n_hgroups * a.max_chunks;
+    ItemGeometry first_geom;
+    first_geom.b = first_geom.hgroup = first_geom.c = first_geom.start = first_geom.end = 0;
+    if ((int)blockIdx.x < total_items) first_geom = decode_item(a, plan, blockIdx.x);
+
     if (threadIdx.x == 0) {
         VTEB_TRACE_CTA(0);
         VTEB_TRACE_LAUNCH(0, a.k_cache, 0, false);
@@ -139,7 +161,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     __syncthreads();
     grid_launch_dependents();
 
-    const int total_items = a.batch * plan.n_hgroups * a.max_chunks;
     const long long pos_stride = 2ll * a.num_kv_heads * D;      // bytes between positions
 
     // ===================================================================== K loader
@@ -152,8 +173,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         bool alive = true;
         while (alive) {
             const bool stop = item >= total_items;
-            ItemGeometry g;
-            if (!stop) g = decode_item(a, plan, item);
+            ItemGeometry g = first_geom;
+            if (!stop && item != (int)blockIdx.x) g = decode_item(a, plan, item);
             const int ntiles = stop ? 1 : max(1, (g.end - g.start + plan.tile - 1) / plan.tile);
             for (int t = 0; t < ntiles; ++t) {
                 VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 0);
@@ -212,6 +233,13 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             if (lane == 0) next = gridDim.x + atomicAdd(a.ticket, 1);
             item = __shfl_sync(0xffffffffu, next, 0);
         }
+        if (a.next_k_cache != nullptr && plan.n_hgroups == 1 && total_items <= (int)gridDim.x && (int)blockIdx.x < total_items) {
+            const ItemGeometry g = first_geom;
+            if (g.end > g.start)
+                prefetch_range_l2(reinterpret_cast<const unsigned char*>(a.next_k_cache) +
+                                      2ll * (long long)g.b * a.kv_batch_stride + (long long)g.start * pos_stride,
+                                  (long long)(g.end - g.start) * pos_stride, lane);
+        }
         if (!dep_done) grid_dependency_wait();
         asm volatile("cp.async.wait_all;" ::: "memory");   // own copies have landed before the warp leaves
         return;
@@ -245,6 +273,13 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             }
             if (hd.flags & kTileStop) break;
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
+        }
+        if (a.next_v_cache != nullptr && plan.n_hgroups == 1 && total_items <= (int)gridDim.x && (int)blockIdx.x < total_items) {
+            const ItemGeometry g = first_geom;
+            if (g.end > g.start)
+                prefetch_range_l2(reinterpret_cast<const unsigned char*>(a.next_v_cache) +
+                                      2ll * (long long)g.b * a.kv_batch_stride + (long long)g.start * pos_stride,
+                                  (long long)(g.end - g.start) * pos_stride, lane);
         }
         if (!dep_done) grid_dependency_wait();
         asm volatile("cp.async.wait_all;" ::: "memory");
@@ -297,12 +332,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
     grid_dependency_wait();
     if (warp == 0) VTEB_TRACE_LAUNCH(0, a.k_cache, 2, false);
-    if (blockIdx.x < total_items) {
-        const int items_per_seq = plan.n_hgroups * a.max_chunks;
-        const int rank = blockIdx.x / items_per_seq;
-        const int hgroup = (blockIdx.x - rank * items_per_seq) / a.max_chunks;
-        load_q(a.seq_order ? a.seq_order[rank] : rank, hgroup);
-    }
+    if ((int)blockIdx.x < total_items) load_q(first_geom.b, first_geom.hgroup);
 
     int trace_tile = 0;
     for (;;) {
@@ -470,31 +500,43 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 const int kvh = hq / group, row = hq - kvh * group;
                 const float* src0 = merge + ((size_t)kvh * group + row) * pitch;        // warp (0 * hg + kvh)
                 const size_t wstride = (size_t)plan.hg * group * pitch;                  // next warp of the same head
+                constexpr int NV = (D + 127) / 128;                                      // float4 columns per lane
+                const bool col_ok = (D >= 128) || lane < D / 4;
+                float mw[kConsumerWarps], lw[kConsumerWarps];
+                float4 ow[kConsumerWarps][NV];
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    const bool on = w < plan.wph;
+                    const float* src = src0 + (on ? w : 0) * wstride;
+                    mw[w] = on ? src[D + 4] : kNeutralM;
+                    lw[w] = on ? src[D + 5] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < NV; ++i)
+                        ow[w][i] = (on && col_ok) ? *reinterpret_cast<const float4*>(src + i * 128 + lane * 4)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
                 float mm = kNeutralM;
-                for (int w = 0; w < plan.wph; ++w) mm = fmaxf(mm, src0[w * wstride + D + 4]);
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) mm = fmaxf(mm, mw[w]);
                 float ll = 0.f;
-                float4 acc[(D + 127) / 128];
+                float4 acc[NV];
 #pragma unroll
-                for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int w = 0; w < plan.wph; ++w) {
-                    const float* src = src0 + w * wstride;
-                    const float wt = fast_exp2(src[D + 4] - mm);
-                    ll = fmaf(src[D + 5], wt, ll);
+                for (int i = 0; i < NV; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                    for (int i = 0; i < (D + 127) / 128; ++i) {
-                        if (D >= 128 || lane < D / 4) {
-                            const float4 x = *reinterpret_cast<const float4*>(src + i * 128 + lane * 4);
-                            acc[i].x = fmaf(x.x, wt, acc[i].x); acc[i].y = fmaf(x.y, wt, acc[i].y);
-                            acc[i].z = fmaf(x.z, wt, acc[i].z); acc[i].w = fmaf(x.w, wt, acc[i].w);
-                        }
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    const float wt = fast_exp2(mw[w] - mm);       // absent warps: exp2(-1e30 - mm) = 0 (or 1 * zeros)
+                    ll = fmaf(lw[w], wt, ll);
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        acc[i].x = fmaf(ow[w][i].x, wt, acc[i].x); acc[i].y = fmaf(ow[w][i].y, wt, acc[i].y);
+                        acc[i].z = fmaf(ow[w][i].z, wt, acc[i].z); acc[i].w = fmaf(ow[w][i].w, wt, acc[i].w);
                     }
                 }
                 const long long stat = stat0 + (long long)hq * a.max_chunks;
-                if (write_o) {
+                if (write_o && col_ok) {
 #pragma unroll
-                    for (int i = 0; i < (D + 127) / 128; ++i)
-                        if (D >= 128 || lane < D / 4)
-                            *reinterpret_cast<float4*>(a.partial_o + stat * D + i * 128 + lane * 4) = acc[i];
+                    for (int i = 0; i < NV; ++i)
+                        *reinterpret_cast<float4*>(a.partial_o + stat * D + i * 128 + lane * 4) = acc[i];
                 }
                 if (lane == 0) {
                     a.partial_m[stat] = empty ? kNeutralM : mm * kLn2;
@@ -517,7 +559,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
         int num_kv_heads, int head_dim, float scale, const int* __restrict__ kv_cache_offset_ptr,     \
         int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
-        const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status)        \
+        const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status,        \
+        const __half* __restrict__ next_k_cache, const __half* __restrict__ next_v_cache)             \
     {                                                                                                 \
         FastArgs a;                                                                                   \
         a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
@@ -526,6 +569,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.kv_offsets = kv_cache_offset_ptr; a.kv_batch_stride = kv_batch_stride;                      \
         a.max_chunks = max_chunks; a.batch = batch; a.min_chunk = min_chunk; a.flags = flags;         \
         a.seq_order = seq_order; a.ticket = ticket; a.status = status;                                \
+        a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM>(a);                                                                    \
     }
