@@ -195,7 +195,8 @@ def run_ours(args, rank, world, local_rank):
     ex = DecodeAttentionExecutor(rt, CodegenEngine(), metadata(cfg), cfg.batch, cfg.max_seq, n_layers,
                                  n_kv_buffers=n_kv, num_splits=args.splits or None, output_f32=True,
                                  programmatic=not args.no_pdl, compat=args.compat,
-                                 prefetch_next_layer=not args.no_prefetch)
+                                 prefetch_next_layer=not args.no_prefetch,
+                                 fused_combine=args.fuse)
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
@@ -278,7 +279,8 @@ def run_ours(args, rank, world, local_rank):
             "config": config_json(cfg, args.workload, lengths, n_layers, n_kv, ex.dispatcher.max_chunks, world,
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
                                    "programmatic_dependent_launch": not args.no_pdl,
-                                   "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1, "kernels": "compat" if args.compat else "fast"}),
+                                   "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1,
+                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else "fast"}),
             "us_per_layer_token": step_s * 1e6 / n_layers / cfg.batch,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
             "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
@@ -329,13 +331,16 @@ def kernel_durations(rt, ex, n_layers, reps=10):
     disp = ex.dispatcher
     name = "flash_attention_split_kv_partial_kernel" if disp.compat else f"vteb_split_kv_partial_d{disp.head_dim}_kernel"
     out = {}
-    for which, key in ((0, "split_us"), (1, "combine_us")):
+    kinds = ((0, "split_us"),) if disp.fused_combine else ((0, "split_us"), (1, "combine_us"))
+    out["combine_us"] = 0.0
+    for which, key in kinds:
         rt.stream_begin_capture()
         try:
             for l in range(n_layers):
                 launches = disp.build_launches(l, ex.tensor_mapping, ex.offsets.ptr, batch=ex.B)[1:]
                 fn, args, grid, block, smem = launches[which]
-                if which == 0 and not disp.compat and ex.B * disp._plan.n_hgroups * disp.max_chunks > grid[0]:
+                if (which == 0 and not disp.compat and not disp.fused_combine
+                        and ex.B * disp._plan.n_hgroups * disp.max_chunks > grid[0]):
                     # more items than CTAs: the work-queue ticket, normally cleared by the
                     # combine launch, has to start from zero
                     rt.memset_async(ctypes.c_void_p(disp.work_ptr), 4, 0, "attn_splitkv_work")
@@ -373,6 +378,7 @@ def main():
     ap.add_argument("--splits", type=int, default=0, help="split count (0 = dispatcher's choice)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")
     ap.add_argument("--device-fill", action="store_true")

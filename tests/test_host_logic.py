@@ -128,7 +128,7 @@ def mapping(layer=0, stride=32768 * 2 * 128):
 
 # ----------------------------------------------------------------------------- dispatcher
 def test_fast_launch_list_shapes_and_signatures():
-    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1)
+    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, fused_combine=False)
     assert d.enabled and not d.compat and d.max_chunks == 148
     launches = d.build_launches(0, mapping(), 0x7200_0000_0000, batch=1)
     assert len(launches) == 3
@@ -150,6 +150,20 @@ def test_fast_launch_list_shapes_and_signatures():
     assert pm.size == 12 * 148 * 4 and po.size == 12 * 148 * 128 * 4
     again = d.build_launches(1, mapping(1), 0x7200_0000_0000, batch=1)
     assert again[1][1][3].value == ap[3].value
+
+
+def test_fused_launch_list_is_append_plus_one_launch():
+    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, output_f32=True, fused_combine=True)
+    assert d.fused_combine
+    launches = d.build_launches(0, mapping(), 0x7200_0000_0000, batch=1)
+    assert len(launches) == 2
+    fp, ap, gp, bp, sp = launches[1]
+    assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_d128_kernel"])
+    assert ap[-1].value == 2 and ap[-2].value == mapping()['blk.0.attention.output']
+    # three KV heads per group cannot use all eight consumer warps: no in-launch combine
+    d2, *_ = make_dispatcher({'attention.head_count': 12, 'attention.head_count_kv': 3, 'attention.key_length': 128},
+                             fused_combine=True)
+    assert not d2.fused_combine and len(d2.build_launches(0, mapping(), 0x7200_0000_0000)) == 3
 
 
 def test_compat_launch_list_is_the_reference_geometry():

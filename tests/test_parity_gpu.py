@@ -318,3 +318,25 @@ def test_two_gpu_kv_range_sharding_over_nccl(cuda_runtime):
     outs = [p.communicate(timeout=240)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r}/2 ok" in o, o[-2000:]
+
+
+def test_fused_combine_variant_matches(cuda_runtime, codegen):
+    """The opt-in single-launch variant (combine after a bounded grid barrier)."""
+    for name in ("ragged_d64", "group8_d128"):
+        cfg, lens = SMALL_CASES[name]
+        q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
+        ref = orc.decode_attention(q, k, v, off)
+        out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=4, min_chunk=0, fused_combine=True)
+        assert_parity(out, ref)
+    cfg = CONFIGS["c1"]
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), 1, cfg.max_seq, 3, n_kv_buffers=1, fused_combine=True)
+    try:
+        for l in range(3):
+            ex.upload_layer(l, q, k, v)
+        for _ in range(3):                       # replays reuse the barrier words
+            out = ex.execute_decode_batch(off)
+            for l in range(3):
+                assert_parity(out[l], np.load(GOLD / "attn_c1.npz")["out"], tight=5e-5)
+    finally:
+        ex.cleanup()

@@ -14,7 +14,8 @@ import ctypes
 P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 _REFERENCE_PARTIAL = [P, P, P, P, P, P, I, I, I, F, P, I, I]
-_FAST_PARTIAL = _REFERENCE_PARTIAL + [I, I, I, P, P, P, P, P]   # batch, min_chunk, flags, seq_order, ticket, status, next K, next V
+_FAST_PARTIAL = _REFERENCE_PARTIAL + [I, I, I, P, P, P, P, P, P, I]
+# ... batch, min_chunk, flags, seq_order, ticket, status, next K, next V, output, out_kind
 _REDUCE = [P, P, P, P, I, I, I]
 _FAST_COMBINE = _REDUCE + [I, P]                          # dsplit, ticket
 

@@ -32,7 +32,8 @@ class DecodeAttentionExecutor:
                  use_graph: bool = True, programmatic: Optional[bool] = None, compat: bool = False,
                  with_append: bool = False, fixed_chunk_size=None, min_chunk: Optional[int] = None,
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
-                 emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True):
+                 emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
+                 fused_combine: Optional[bool] = None):
         self.hip = hip
         self.metadata = dict(metadata)
         self.B = int(batch_size)
@@ -74,7 +75,7 @@ class DecodeAttentionExecutor:
             hip, codegen, self.metadata, allocator=allocator, context_length=self.S, batch_size=self.B,
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
-            prefetch_next_layer=prefetch_next_layer)
+            prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine)
 
         A = allocator.allocate
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
@@ -165,7 +166,8 @@ class DecodeAttentionExecutor:
         self.hip.programmatic_launch = self.programmatic
         try:
             if not self.use_graph:
-                self.kernel_launches_per_step = (3 if self.with_append else 2) * self.L
+                per_layer = (1 if self.dispatcher.fused_combine else 2) + (1 if self.with_append else 0)
+                self.kernel_launches_per_step = per_layer * self.L
                 return
             self.hip.stream_begin_capture()
             try:

@@ -303,23 +303,33 @@ extern "C" __global__ void flash_attention_split_kv_reduce_f32_kernel(
 // splits get weight 0 and their partial_o is never used.  CTA 0 also clears the
 // work-queue ticket so the next split launch starts from zero.
 // ---------------------------------------------------------------------------
-template <typename OutT, bool kEmitState = false>
-__device__ __forceinline__ void fast_combine_body(
+// kFused: called from inside the split kernel by its 256 consumer threads after a
+// grid-wide barrier; CTA-wide synchronisation then uses named barrier 1 (the loader
+// warps have left) and partials are read with L2-only loads.
+template <bool kFused>
+__device__ __forceinline__ void combine_sync() {
+    if constexpr (kFused) asm volatile("bar.sync 1, 256;" ::: "memory");
+    else __syncthreads();
+}
+
+template <bool kFused>
+__device__ __forceinline__ float combine_ld(const float* p) { return kFused ? __ldcg(p) : *p; }
+template <bool kFused>
+__device__ __forceinline__ float4 combine_ld4(const float* p) {
+    return kFused ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p);
+}
+
+// out_kind: 1 = fp16 output, 2 = fp32 output, 3 = unnormalised shard state [D + 2] per row
+template <bool kFused>
+__device__ __forceinline__ void combine_slice(
     const float* __restrict__ partial_m, const float* __restrict__ partial_l,
-    const float* __restrict__ partial_o, OutT* __restrict__ output,
-    int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
+    const float* __restrict__ partial_o, void* __restrict__ output, int out_kind,
+    int head_dim, int max_chunks, int dsplit, int slice, float* weight_sh)
 {
-    extern __shared__ float weight_sh[];           // [max_chunks]
     __shared__ float red_max[8], red_sum[8];
     __shared__ float4 acc_sh[8][8];                // [warp][q]
-    VTEB_TRACE_LAUNCH(1, output, 0, false);
-    grid_launch_dependents();
-    grid_dependency_wait();
-    VTEB_TRACE_LAUNCH(1, output, 2, false);
-    if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
-
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int bh = blockIdx.x / dsplit, dpart = blockIdx.x - bh * dsplit;
+    const int bh = slice / dsplit, dpart = slice - bh * dsplit;
     const long long base = (long long)bh * max_chunks;
     const int r = tid >> 3, q = tid & 7;
     const float* o_base = partial_o + base * head_dim + dpart * 32 + q * 4;
@@ -330,22 +340,21 @@ __device__ __forceinline__ void fast_combine_body(
     // with the usual running-maximum rescale.
     for (int c0 = 0; c0 < max_chunks; c0 += 256) {
         const int cm = c0 + tid;
-        const float my_m = (cm < max_chunks) ? partial_m[base + cm] : kNeutralM;
-        const float my_l = (cm < max_chunks) ? partial_l[base + cm] : 0.f;
+        const float my_m = (cm < max_chunks) ? combine_ld<kFused>(partial_m + base + cm) : kNeutralM;
+        const float my_l = (cm < max_chunks) ? combine_ld<kFused>(partial_l + base + cm) : 0.f;
         float4 o[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const int c = c0 + r + 32 * k;
-            o[k] = (c < max_chunks) ? *reinterpret_cast<const float4*>(o_base + (long long)c * head_dim)
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            o[k] = (c < max_chunks) ? combine_ld4<kFused>(o_base + (long long)c * head_dim) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         // ---- maximum of this pass
         float mx = my_m;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        __syncthreads();                            // previous pass is done with red_* and weight_sh
+        combine_sync<kFused>();                     // previous pass / slice is done with red_* and weight_sh
         if (lane == 0) red_max[warp] = mx;
-        __syncthreads();
+        combine_sync<kFused>();
         float pass_max = red_max[0];
 #pragma unroll
         for (int w = 1; w < 8; ++w) pass_max = fmaxf(pass_max, red_max[w]);
@@ -359,7 +368,7 @@ __device__ __forceinline__ void fast_combine_body(
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, off);
         if (lane == 0) red_sum[warp] = ls;
-        __syncthreads();
+        combine_sync<kFused>();
         float pass_l = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) pass_l += red_sum[w];
@@ -384,22 +393,39 @@ __device__ __forceinline__ void fast_combine_body(
         acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
     }
     if (lane < 8) acc_sh[warp][lane] = acc;
-    __syncthreads();
+    combine_sync<kFused>();
     if (tid < 32) {
         const float* flat = reinterpret_cast<const float*>(acc_sh);
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) s += flat[w * 32 + tid];
-        if constexpr (kEmitState) {
+        if (out_kind == 3) {
             // unnormalised state of this shard: o[D], then m (natural-log units), then l
             float* st = reinterpret_cast<float*>(output) + (long long)bh * (head_dim + 2);
             st[dpart * 32 + tid] = s;
             if (dpart == 0 && tid == 0) { st[head_dim] = M; st[head_dim + 1] = lsum; }
         } else {
-            const float L = fmaxf(lsum, 1e-20f);
-            output[(long long)bh * head_dim + dpart * 32 + tid] = to_out<OutT>(s / L);
+            const float v = s / fmaxf(lsum, 1e-20f);
+            const long long idx = (long long)bh * head_dim + dpart * 32 + tid;
+            if (out_kind == 2) reinterpret_cast<float*>(output)[idx] = v;
+            else reinterpret_cast<__half*>(output)[idx] = __float2half(v);
         }
     }
+}
+
+__device__ __forceinline__ void fast_combine_kernel_body(
+    const float* __restrict__ partial_m, const float* __restrict__ partial_l,
+    const float* __restrict__ partial_o, void* __restrict__ output, int out_kind,
+    int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
+{
+    extern __shared__ float combine_weight_sh[];   // [min(max_chunks, 256)]
+    VTEB_TRACE_LAUNCH(1, output, 0, false);
+    grid_launch_dependents();
+    grid_dependency_wait();
+    VTEB_TRACE_LAUNCH(1, output, 2, false);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
+    combine_slice<false>(partial_m, partial_l, partial_o, output, out_kind, head_dim, max_chunks, dsplit,
+                         blockIdx.x, combine_weight_sh);
     VTEB_TRACE_LAUNCH(1, output, 1, true);
 }
 
@@ -408,7 +434,7 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f16_kern
     const float* __restrict__ partial_o, __half* __restrict__ output,
     int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
-    fast_combine_body<__half>(partial_m, partial_l, partial_o, output, num_q_heads, head_dim, max_chunks, dsplit, ticket);
+    fast_combine_kernel_body(partial_m, partial_l, partial_o, output, 1, head_dim, max_chunks, dsplit, ticket);
 }
 
 extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f32_kernel(
@@ -416,7 +442,7 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f32_kern
     const float* __restrict__ partial_o, float* __restrict__ output,
     int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
-    fast_combine_body<float>(partial_m, partial_l, partial_o, output, num_q_heads, head_dim, max_chunks, dsplit, ticket);
+    fast_combine_kernel_body(partial_m, partial_l, partial_o, output, 2, head_dim, max_chunks, dsplit, ticket);
 }
 
 // ---------------------------------------------------------------------------
@@ -433,7 +459,7 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_state_ke
     const float* __restrict__ partial_o, float* __restrict__ state,
     int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
-    fast_combine_body<float, true>(partial_m, partial_l, partial_o, state, num_q_heads, head_dim, max_chunks, dsplit, ticket);
+    fast_combine_kernel_body(partial_m, partial_l, partial_o, state, 3, head_dim, max_chunks, dsplit, ticket);
 }
 
 // gathered: [n_shards][rows][D + 2]; out: [rows][D] fp32.  grid (rows, 1, 1), block (D, 1, 1).

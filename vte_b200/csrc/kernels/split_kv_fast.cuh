@@ -36,6 +36,7 @@ struct FastArgs {
     const int* kv_offsets; long long kv_batch_stride; int max_chunks;
     int batch, min_chunk, flags; const int* seq_order; int* ticket; int* status;
     const __half* next_k_cache; const __half* next_v_cache;   // optional: the next layer's caches, for L2 prefetch
+    void* output; int out_kind;   // out_kind != 0: combine inside this launch (1 fp16, 2 fp32, 3 shard state)
 };
 
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
@@ -45,6 +46,8 @@ constexpr int kBarFull = 0;                        // 8 barriers
 constexpr int kBarEmpty = 8 * kMaxStages;          // 8 barriers
 constexpr int kBarHeader = 16 * kMaxStages;        // 8 barriers: header published (K loader -> V loader)
 constexpr int kBarMerge = 24 * kMaxStages;         // 2 barriers
+constexpr int kBarFinal = 24 * kMaxStages + 16;    // 2 barriers: CTA's partials stored / grid barrier passed
+constexpr int kGridOkOffset = 260;                 // int: result of the grid barrier
 constexpr int kAbortOffset = 256;
 constexpr int kHeaderOffset = 512;
 
@@ -97,6 +100,28 @@ __device__ __forceinline__ void prefetch_range_l2(const unsigned char* base, lon
         const unsigned n = (unsigned)((bytes - off < kPiece) ? (bytes - off) : kPiece) & ~15u;
         if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
     }
+}
+
+// Grid-wide barrier for a grid whose CTAs are all resident (grid <= SM count, one CTA
+// per SM).  words[0] counts arrivals and is cleared by the last arriver, words[1] is a
+// generation number; one thread per CTA calls this.  The wait is bounded (~2 s).
+__device__ __forceinline__ bool grid_barrier_bounded(int* words, int n_ctas) {
+    volatile int* gen = words + 1;
+    const int my_gen = *gen;
+    __threadfence();
+    const int old = atomicAdd(words, 1);
+    if (old == n_ctas - 1) {
+        words[0] = 0;
+        __threadfence();
+        atomicAdd(words + 1, 1);
+        return true;
+    }
+    const long long t0 = clock64();
+    while (*gen == my_gen) {
+        if (clock64() - t0 > 4000000000ll) return false;
+    }
+    __threadfence();
+    return true;
 }
 
 struct ItemGeometry {
@@ -155,6 +180,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
         mbar_init(merge_bar0, plan.active_warps);
         mbar_init(merge_bar0 + 8, plan.active_warps);
+        mbar_init(bar0 + kBarFinal, plan.active_warps);
+        mbar_init(bar0 + kBarFinal + 8, 1);
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -550,6 +577,34 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
         }
     }
+
+    if (a.out_kind == 0) return;
+    // ===================================================================== in-launch combine
+    // (needs all eight consumer warps; the host only asks for it then)
+    // 1. every consumer warp's partial stores are fenced, then counted on a CTA barrier
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar0 + kBarFinal);
+    if (!mbar_wait_bounded(bar0 + kBarFinal, 0, abort_word)) {
+        raise_abort(abort_word, a.status, kStatusMergeTimeout);
+        return;
+    }
+    // 2. one thread waits until every CTA of the grid has done the same
+    volatile int* grid_ok = reinterpret_cast<volatile int*>(smem_raw + kGridOkOffset);
+    if (warp == 0 && lane == 0) {
+        *grid_ok = grid_barrier_bounded(a.ticket + 2, gridDim.x) ? 1 : 0;
+        mbar_arrive(bar0 + kBarFinal + 8);
+    }
+    if (!mbar_wait_bounded(bar0 + kBarFinal + 8, 0, abort_word) || *grid_ok == 0) {
+        raise_abort(abort_word, a.status, kStatusGridTimeout);
+        return;
+    }
+    // 3. the grid's CTAs share the (sequence, head, 32-column) slices of the combine
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.ticket = 0;     // work queue starts from zero next launch
+    const int dsplit = D / 32;
+    const int n_slices = a.batch * a.num_q_heads * dsplit;
+    for (int slice = blockIdx.x; slice < n_slices; slice += gridDim.x)
+        combine_slice<true>(a.partial_m, a.partial_l, a.partial_o, a.output, a.out_kind, D, a.max_chunks, dsplit, slice, merge);
 }
 
 #define VTEB_FAST_PARTIAL(NAME, DIM)                                                                  \
@@ -560,7 +615,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         int num_kv_heads, int head_dim, float scale, const int* __restrict__ kv_cache_offset_ptr,     \
         int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
         const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status,        \
-        const __half* __restrict__ next_k_cache, const __half* __restrict__ next_v_cache)             \
+        const __half* __restrict__ next_k_cache, const __half* __restrict__ next_v_cache,             \
+        void* __restrict__ output, int out_kind)                                                      \
     {                                                                                                 \
         FastArgs a;                                                                                   \
         a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
@@ -570,6 +626,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.max_chunks = max_chunks; a.batch = batch; a.min_chunk = min_chunk; a.flags = flags;         \
         a.seq_order = seq_order; a.ticket = ticket; a.status = status;                                \
         a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
+        a.output = output; a.out_kind = out_kind;                                                     \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM>(a);                                                                    \
     }

@@ -19,7 +19,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kNeutralM = -1e30f;                      // reference's "empty split" maximum
 #ifndef VTEB_SMEM_BUDGET_KB
-#define VTEB_SMEM_BUDGET_KB 227
+#define VTEB_SMEM_BUDGET_KB 225   /* 227 KB per CTA minus the split kernel's static shared memory */
 #endif
 constexpr int kSmemBudget = VTEB_SMEM_BUDGET_KB * 1024;  // dynamic shared memory the split kernel may use
 
@@ -29,6 +29,7 @@ constexpr int kStatusOk = 0;
 constexpr int kStatusFullTimeout = 1;    // consumer never saw a tile arrive
 constexpr int kStatusEmptyTimeout = 2;   // loader never got a stage back
 constexpr int kStatusMergeTimeout = 3;   // cross-warp merge barrier never completed
+constexpr int kStatusGridTimeout = 4;    // another CTA never reached the grid-wide barrier
 
 // Tile flags carried in the per-stage header.
 constexpr int kTileFirst = 1;   // first tile of a work item: reset state, fetch Q

@@ -575,7 +575,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     if (n_ctas > items) n_ctas = (int)items;
 
     typedef void (*FastKernel)(const __half*, const __half*, const __half*, float*, float*, float*, int, int,
-                               int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*, const __half*);
+                               int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*, const __half*, void*, int);
     FastKernel fk;
     int slot;
     if (head_dim == 64) { fk = vteb_split_kv_partial_d64_kernel; slot = 0; }
@@ -590,7 +590,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     rc = launch_rt(fk, dim3(n_ctas), dim3(vteb::kFastThreads), (size_t)p.smem_bytes, s, pdl, qh, kh, vh,
                    partial_m, partial_l, partial_o, num_q_heads, num_kv_heads, head_dim, scale, kv_offsets,
                    (int)kv_batch_stride, max_chunks, batch, min_chunk, kflags, (const int*)nullptr, work,
-                   work + 1, (const __half*)nullptr, (const __half*)nullptr);
+                   work + 1, (const __half*)nullptr, (const __half*)nullptr, (void*)nullptr, 0);
     if (rc) return rc;
 
     vteb_fast_plan hp;
