@@ -185,6 +185,20 @@ def run_ours(args, rank, world, local_rank):
     cfg = CONFIGS[args.workload]
     lengths = draw_context_lengths(cfg)
     n_layers = args.layers or cfg.layers
+    partition = args.partition or "replicas"
+    if world == 1:
+        partition = "single GPU"
+    if partition == "kv-range":
+        return run_kv_range(args, rank, world, local_rank, rdzv, cfg, n_layers)
+    global_cfg, global_lengths = cfg, lengths
+    if partition == "sequences":
+        from dataclasses import replace
+        from vte_b200.core.kv_shard import sequences_of_rank
+        first, last = sequences_of_rank(cfg.batch, rank, world)
+        if last <= first:
+            raise SystemExit(f"rank {rank} got no sequence: batch {cfg.batch} over {world} ranks")
+        lengths = lengths[first:last]
+        cfg = replace(cfg, batch=last - first)
     rt = CudaRuntime(device_index=local_rank)
     rt.initialize()
     free_b, total_b = rt.get_real_mem_info()
@@ -194,13 +208,14 @@ def run_ours(args, rank, world, local_rank):
         n_kv = min(n_kv, args.kv_buffers)
     ex = DecodeAttentionExecutor(rt, CodegenEngine(), metadata(cfg), cfg.batch, cfg.max_seq, n_layers,
                                  n_kv_buffers=n_kv, num_splits=args.splits or None, output_f32=True,
+                                 min_chunk=None if args.min_chunk < 0 else args.min_chunk,
                                  programmatic=not args.no_pdl, compat=args.compat,
                                  prefetch_next_layer=not args.no_prefetch,
                                  fused_combine=args.fuse)
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
-    host_gen = kv_layer_bytes * n_kv <= (2 << 30) and not args.device_fill
+    host_gen = kv_layer_bytes * n_kv <= (2 << 30) and not args.device_fill and partition != "sequences"
     for l in range(n_layers):
         if host_gen and l < n_kv:
             q, k, v, off = make_layer_inputs(cfg, l)
@@ -220,7 +235,9 @@ def run_ours(args, rank, world, local_rank):
     ex._update_staging_buffers(offsets)
     rt.stream_synchronize()
 
-    bytes_step = algorithmic_bytes(cfg, lengths) * n_layers
+    bytes_step = algorithmic_bytes(cfg, lengths) * n_layers          # this rank's share
+    bytes_all = (algorithmic_bytes(global_cfg, global_lengths) * n_layers if partition == "sequences"
+                 else bytes_step * world)
     # ---- parity of what is being timed (layer 0 against the oracle)
     parity = None
     out = ex.execute_decode_batch(offsets)
@@ -267,21 +284,22 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         peak_gbs, peak_kind = measured_peaks()
         step_s = ms_max / 1e3 / args.steps
-        value = bytes_step * world / step_s / 1e12
-        e2e_value = bytes_step * world / (e2e_s / args.steps) / 1e12
+        value = bytes_all / step_s / 1e12
+        e2e_value = bytes_all / (e2e_s / args.steps) / 1e12
         split_bytes = bytes_step / n_layers
         split_s = kern["split_us"] * 1e-6
         achieved = split_bytes / split_s / 1e9
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "strong" if partition == "sequences" else "weak", "vs_baseline": None,
             "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
             "config": config_json(cfg, args.workload, lengths, n_layers, n_kv, ex.dispatcher.max_chunks, world,
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
                                    "programmatic_dependent_launch": not args.no_pdl,
                                    "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1,
                                    "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else "fast"}),
-            "us_per_layer_token": step_s * 1e6 / n_layers / cfg.batch,
+            "us_per_layer_token": step_s * 1e6 / n_layers / global_cfg.batch,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
             "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
             "e2e": {"value": e2e_value, "unit": UNIT,
@@ -318,6 +336,75 @@ def run_ours(args, rank, world, local_rank):
     rdzv.close()
     if rank == 0:
         print(json.dumps(result), flush=True)
+    return 0
+
+
+def run_kv_range(args, rank, world, local_rank, rdzv, cfg, n_layers):
+    """One sequence whose KV range is split evenly over the ranks: per layer split ->
+    state combine -> NCCL all-gather of (o, m, l) -> merge, all in one graph per rank."""
+    from vte_b200.bridge import CudaRuntime
+    from vte_b200.bridge.nccl import NcclCommunicator
+    from vte_b200.compiler import CodegenEngine
+    from vte_b200.core.kv_shard import KVRangeShardedDecode, kv_range_of_rank
+    if cfg.batch != 1:
+        raise SystemExit("kv-range partition is for a single sequence")
+    total = cfg.ctx_max
+    lo, hi = kv_range_of_rank(total, rank, world)
+    rt = CudaRuntime(device_index=local_rank)
+    rt.initialize()
+    comm = NcclCommunicator(rt, rank, world, rdzv)
+    sh = KVRangeShardedDecode(rt, CodegenEngine(), metadata(cfg), hi - lo, n_layers, comm, num_splits=args.splits or None,
+                              programmatic=not args.no_pdl)
+    for l in range(n_layers):
+        sh.ex.fill_cache_on_device(l, cfg.base_seed * 1000 + l * world + rank, cfg.sigma_kv)
+        rng = np.random.default_rng([cfg.base_seed, l, 99])
+        sh.ex.upload_layer(l, rng.standard_normal((1, cfg.num_q_heads, cfg.head_dim), dtype=np.float32).astype(np.float16))
+    out = sh.execute_decode(hi - lo - 1)
+    finite = bool(np.all(np.isfinite(out)))
+    for _ in range(max(3, args.warmup)):
+        sh.launch_step()
+    rt.synchronize()
+    rdzv.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = rt.event_create(), rt.event_create()
+    rt.event_record(e0)
+    for _ in range(args.steps):
+        sh.launch_step()
+    rt.event_record(e1)
+    rt.synchronize()
+    ms = rdzv.max_float(rt.event_elapsed_ms(e0, e1))
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        sh.execute_decode(hi - lo - 1)
+    e2e_s = rdzv.max_float(time.perf_counter() - t0)
+    clocks = sampler.stop()
+    lengths = np.array([total], dtype=np.int32)
+    bytes_all = algorithmic_bytes(cfg, lengths) * n_layers
+    step_s = ms / 1e3 / args.steps
+    if rank == 0:
+        peak_gbs, peak_kind = measured_peaks()
+        value = bytes_all / step_s / 1e12
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(3, args.warmup), "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+                "config": config_json(cfg, args.workload, lengths, n_layers, n_layers, sh.ex.dispatcher.max_chunks, world,
+                                      {"partition": f"KV range split over {world} GPUs, NCCL all-gather of "
+                                                    f"{sh.state_floats * 4} bytes per rank per layer",
+                                       "input_generation": "device fill (counter-based normal)"}),
+                "us_per_layer_token": step_s * 1e6 / n_layers,
+                "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
+                "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
+                "e2e": {"value": bytes_all / (e2e_s / args.steps) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 4,
+                        "d2h_bytes_per_step": int(n_layers * sh.rows * cfg.head_dim * 4)},
+                "gpu_launches": sh.ex.kernel_launches_per_step * args.steps, "clocks": clocks,
+                "parity": {"finite": finite, "note": "parity of this path is asserted by the tests"}}
+        print(json.dumps(line), flush=True)
+    sh.cleanup()
+    comm.destroy()
+    rt.cleanup()
+    rdzv.barrier()
+    rdzv.close()
     return 0
 
 
@@ -376,7 +463,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count")
     ap.add_argument("--kv-buffers", type=int, default=0, help="distinct KV caches to cycle through")
     ap.add_argument("--splits", type=int, default=0, help="split count (0 = dispatcher's choice)")
+    ap.add_argument("--min-chunk", type=int, default=-1, help="minimum positions per split (-1 = dispatcher's choice)")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
+    ap.add_argument("--partition", default="", choices=["", "replicas", "sequences", "kv-range"],
+                    help="with N > 1: replicas (each rank its own copy, weak; default), sequences (the batch is split "
+                         "over the ranks, strong), kv-range (one sequence's KV range split over the ranks, NCCL all-gather)")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")

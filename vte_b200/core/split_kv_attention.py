@@ -29,7 +29,7 @@ from ..config import ENV_COMPAT_KERNELS, ENV_DISABLE_SPLITKV
 
 SPLIT_KV_CHUNK_SIZE = 32          # the reference's historical chunk (RX 7600, 32 CUs)
 MAX_SPLITS = 256
-TARGET_CHUNK_POSITIONS = 256      # chunk length aimed at when many sequences share the GPU
+TARGET_CHUNK_POSITIONS = 256      # smallest chunk length aimed at when many sequences share the GPU
 FLAG_WRITE_EMPTY_O = 1
 
 
@@ -41,20 +41,35 @@ def _chunk_size_for_cus(num_cus: int) -> int:
     return max(8, min(64, round(1024 / num_cus)))
 
 
+def choose_chunk_positions(num_sms: int, batch: int, n_hgroups: int, context_length: int) -> int:
+    """Positions per split aimed at when several sequences share the GPU: about four
+    work items per SM if every sequence were half the configured context, as a power of
+    two within [256, 2048].  Measured on B200: a work item costs a few microseconds of
+    fixed time (cross-warp merge, next item's Q fetch), so 256-position items reach
+    2.9 TB/s on the 16 x (2 KV heads of 256) workload where 2048-position items reach 4.1."""
+    est_positions = batch * n_hgroups * max(1, context_length // 2)
+    target = est_positions / max(1, num_sms * 4)
+    chunk = TARGET_CHUNK_POSITIONS
+    while chunk < target and chunk < 2048:
+        chunk *= 2
+    return chunk
+
+
 def choose_split_count(num_sms: int, batch: int, n_hgroups: int, context_length: int) -> int:
     """Split count when the caller does not fix one.
 
     One sequence: as many splits as SMs, so the persistent grid is exactly one
-    wave of equal work items.  Several sequences: chunks of about 256 positions
-    (capped at 256 splits for the longest context), so that ragged lengths
-    balance through the work queue while the fp32 partials stay a few percent
-    of the K/V bytes.
+    wave of equal work items.  Several sequences: chunks of
+    `choose_chunk_positions` (capped at 256 splits for the longest context), so
+    that ragged lengths balance through the work queue while the fp32 partials
+    stay a few percent of the K/V bytes.
     """
     if batch * n_hgroups <= 1:
         return max(1, min(MAX_SPLITS, num_sms))
     if batch == 1:
         return max(1, min(MAX_SPLITS, num_sms // n_hgroups))
-    return max(1, min(MAX_SPLITS, math.ceil(context_length / TARGET_CHUNK_POSITIONS)))
+    chunk = choose_chunk_positions(num_sms, batch, n_hgroups, context_length)
+    return max(1, min(MAX_SPLITS, math.ceil(context_length / chunk)))
 
 
 class SplitKVAttentionDispatcher:
@@ -115,7 +130,9 @@ class SplitKVAttentionDispatcher:
                 raise CudaSafetyError(f"split count {self.max_chunks} outside 1..65535")
             self.chunk_size = 0
         if min_chunk is None:
-            min_chunk = TARGET_CHUNK_POSITIONS if (self.batch_size > 1 and not self.fixed_chunk) else 0
+            n_hg = self._plan.n_hgroups if (self._plan is not None and self._plan.ok) else self.num_kv_heads
+            min_chunk = (choose_chunk_positions(num_cus, self.batch_size, n_hg, self.context_length)
+                         if (self.batch_size > 1 and not self.fixed_chunk) else 0)
         self.min_chunk = int(min_chunk)
 
         self._kernel_cache = {}
