@@ -340,3 +340,61 @@ def test_fused_combine_variant_matches(cuda_runtime, codegen):
                 assert_parity(out[l], np.load(GOLD / "attn_c1.npz")["out"], tight=5e-5)
     finally:
         ex.cleanup()
+
+
+def _device_filled_case(rt, codegen, cfg, lengths, seed, **kw):
+    """Executor whose caches were generated on the device; returns (executor, q)."""
+    ex = DecodeAttentionExecutor(rt, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 1, **kw)
+    ex.fill_cache_on_device(0, seed, cfg.sigma_kv, cfg.outlier_frac, cfg.outlier_scale)
+    rng = np.random.default_rng([cfg.base_seed, 77])
+    q = rng.standard_normal((cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float32).astype(np.float16)
+    ex.upload_layer(0, q)
+    return ex, q
+
+
+@pytest.mark.parametrize("name", ["c3", "c4"])
+def test_full_size_ragged_batches(cuda_runtime, codegen, name):
+    """Configs 3 and 4 at their full sizes (2.1 GB of cache per layer, generated on the
+    device): the result must not depend on the split count, and a sample of sequences
+    (shortest, longest, two more) downloaded from the device must match the oracle."""
+    from vte_b200.workloads import draw_context_lengths
+    cfg = CONFIGS[name]
+    lengths = draw_context_lengths(cfg)
+    off = (lengths - 1).astype(np.int32)
+    outs = []
+    for kw in ({}, {"num_splits": 37, "min_chunk": 0}):
+        ex, q = _device_filled_case(cuda_runtime, codegen, cfg, lengths, 4242, **kw)
+        try:
+            outs.append(ex.execute_decode_batch(off)[0])
+            if not kw:
+                sample = sorted({int(np.argmin(lengths)), int(np.argmax(lengths)), 1, cfg.batch - 1})
+                for b in sample:
+                    k, v = ex.download_cache_rows(0, b, int(lengths[b]))
+                    ref = orc.decode_attention(q[b:b + 1], k[None], v[None], off[b:b + 1])
+                    max_abs, rel = orc.parity_metrics(outs[0][b:b + 1], ref)
+                    assert max_abs <= MAX_ABS and rel <= REL_L2, (name, b, max_abs, rel)
+                    assert max_abs <= 1e-3, (name, b, max_abs)
+        finally:
+            ex.cleanup()
+    assert np.all(np.isfinite(outs[0]))
+    max_abs, rel = orc.parity_metrics(outs[1], outs[0])
+    assert max_abs <= 2e-4 and rel <= 1e-3, (max_abs, rel)
+
+
+def test_one_million_context(cuda_runtime, codegen):
+    """Config 5's sequence on one GPU (1,048,576 positions, 1 GB of cache, device-generated):
+    148 splits against 8 splits, and against the oracle on the downloaded cache."""
+    cfg = CONFIGS["c5"]
+    off = np.array([cfg.ctx_max - 1], dtype=np.int32)
+    outs = []
+    for kw in ({}, {"num_splits": 8}):
+        ex, q = _device_filled_case(cuda_runtime, codegen, cfg, None, 555, **kw)
+        try:
+            outs.append(ex.execute_decode_batch(off)[0])
+            if not kw:
+                k, v = ex.download_cache_rows(0, 0, cfg.ctx_max)
+                ref = orc.decode_attention(q, k[None], v[None], off)
+                assert_parity(outs[0], ref, tight=1e-5)
+        finally:
+            ex.cleanup()
+    assert np.max(np.abs(outs[0] - outs[1])) < 1e-5
