@@ -87,6 +87,8 @@ int vteb_module_load(void** module, const char* cubin_path);
 int vteb_module_get_function(void** function, void* module, const char* name);
 int vteb_module_unload(void* module);
 int vteb_func_set_max_dynamic_smem(void* function, int bytes);
+/* Preferred shared-memory carve-out of the function, percent of the maximum (CUDA only). */
+int vteb_func_set_shared_carveout(void* function, int percent);
 int vteb_launch(void* function, unsigned gx, unsigned gy, unsigned gz,
                 unsigned bx, unsigned by, unsigned bz,
                 unsigned shared_mem_bytes, void* stream, void** params, unsigned flags);
@@ -139,6 +141,9 @@ typedef struct vteb_fast_plan {
     int combine_smem_bytes; /* per split, up to 256 splits: min(max_chunks, 256) * this */
 } vteb_fast_plan;
 int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
+/* Columns per lane of the short-list combine kernel (split counts up to 64): a warp
+ * merges 32 * epl columns of one (sequence, head) row. */
+int vteb_combine_rows_epl(int rows, int head_dim);
 
 /* One layer's decode attention for a batch: split kernel then combine.
  *   q [batch, Hq, D] fp16; k_cache, v_cache [batch, max_seq, Hkv, D] fp16 with

@@ -84,6 +84,7 @@ class FakeRuntime:
 
     def get_num_cus(self): return self.sms
     def get_gpu_architecture(self): return "sm_100a"
+    def combine_rows_epl(self, rows, d): return self._lib.vteb_combine_rows_epl(rows, d)
     def split_kv_plan(self, hq, hkv, d):
         plan = FastPlan()
         self._lib.vteb_split_kv_plan(hq, hkv, d, ctypes.byref(plan))

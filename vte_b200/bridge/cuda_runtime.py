@@ -94,6 +94,7 @@ def _declare(lib):
         "vteb_module_get_function": (i, [vpp, vp, ctypes.c_char_p]),
         "vteb_module_unload": (i, [vp]),
         "vteb_func_set_max_dynamic_smem": (i, [vp, i]),
+        "vteb_func_set_shared_carveout": (i, [vp, i]),
         "vteb_launch": (i, [vp, u, u, u, u, u, u, u, vp, vpp, u]),
         "vteb_stream_create": (i, [vpp]),
         "vteb_stream_destroy": (i, [vp]),
@@ -116,6 +117,7 @@ def _declare(lib):
         "vteb_nccl_all_reduce_max_f32": (i, [vp, vp, vp, sz, vp]),
         "vteb_nccl_comm_destroy": (i, [vp]),
         "vteb_split_kv_plan": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
+        "vteb_combine_rows_epl": (i, [i, i]),
         "vteb_split_kv_decode": (i, [vp, vp, vp, vp, vp, i, vp, vp, vp, vp, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_split_kv_decode_noalloc": (i, [vp, vp, vp, vp, vp, i, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_kv_cache_append": (i, [vp, vp, vp, vp, vp, i, i, i, ll, vp]),
@@ -449,6 +451,10 @@ class CudaRuntime:
         from ..compiler.signatures import KERNEL_SIGNATURES
         if kernel_name in KERNEL_SIGNATURES:
             self._signatures[function.value] = (kernel_name, len(KERNEL_SIGNATURES[kernel_name]))
+            # Every kernel of the attention path asks for the same (maximum) shared-memory
+            # carve-out: the SMs then never have to drain to re-split L1 / shared memory
+            # between the split launch and the small launches around it.
+            self._check_error(self._lib.vteb_func_set_shared_carveout(function, 100), "cuFuncSetAttribute")
         return module, function
 
     def register_kernel_signature(self, function, name: str, n_args: int) -> None:
@@ -610,6 +616,9 @@ class CudaRuntime:
         self._check_error(self._lib.vteb_split_kv_plan(num_q_heads, num_kv_heads, head_dim, ctypes.byref(plan)),
                           "vteb_split_kv_plan")
         return plan
+
+    def combine_rows_epl(self, rows: int, head_dim: int) -> int:
+        return int(self._lib.vteb_combine_rows_epl(int(rows), int(head_dim)))
 
     def split_kv_decode(self, q, k_cache, v_cache, kv_offsets, output, out_is_f32: bool, partial_m, partial_l,
                         partial_o, work, batch: int, num_q_heads: int, num_kv_heads: int, head_dim: int,

@@ -136,6 +136,7 @@ class SplitKVAttentionDispatcher:
         self.min_chunk = int(min_chunk)
 
         self._kernel_cache = {}
+        self._rows_combine = False
         self._partial_m = self._partial_l = self._partial_o = self._work = None
         self.enabled = not bool(os.environ.get(ENV_DISABLE_SPLITKV)) and allocator is not None
 
@@ -183,8 +184,12 @@ class SplitKVAttentionDispatcher:
                     else 'flash_attention_split_kv_reduce_kernel')
             else:
                 self._kernel_cache['partial'] = load('decode_attention', f'vteb_split_kv_partial_d{self.head_dim}_kernel')
+                # short split lists (batched decode): one warp per (sequence, head) row;
+                # long ones (one sequence spread over every SM): one CTA per 32 columns
+                self._rows_combine = self.max_chunks <= 64
                 self._kernel_cache['reduce'] = load(
                     'decode_attention',
+                    'vteb_split_kv_combine_rows_kernel' if self._rows_combine else
                     'vteb_split_kv_combine_state_kernel' if self.emit_state else
                     'vteb_split_kv_combine_f32_kernel' if self.output_f32 else 'vteb_split_kv_combine_f16_kernel')
 
@@ -286,6 +291,12 @@ class SplitKVAttentionDispatcher:
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
         if self.fused_combine:
             return [append, partial]
+        if self._rows_combine:
+            rows = batch * Hq
+            epl = self.hip.combine_rows_epl(rows, D)
+            units = rows * (D // (32 * epl))
+            combine_args = reduce_args + [ci(out_kind), vp(self._work.ptr), ci(rows), ci(epl)]
+            return [append, partial, (reduce_fn, combine_args, ((units + 7) // 8, 1, 1), (256, 1, 1), 0)]
         dsplit = plan.combine_dsplit
         combine_args = reduce_args + [ci(dsplit), vp(self._work.ptr)]
         combine_smem = min(C, 256) * 4

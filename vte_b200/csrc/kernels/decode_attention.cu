@@ -446,6 +446,119 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f32_kern
 }
 
 // ---------------------------------------------------------------------------
+// Combine for short split lists (max_chunks <= 64), as batched decode produces:
+// one warp per (sequence, query head) row, eight rows per CTA, no shared memory
+// and no CTA-wide barrier.  Lane c holds the m and l of splits c and c + 32; the
+// lane owns head_dim / 32 consecutive output columns and walks the splits eight
+// at a time with all loads of a group in flight.  A warp covers 32 * epl columns
+// of a row (epl in {1, 2, 4, 8}, chosen by the host so that a few thousand warps
+// exist); grid (ceil(B * Hq * head_dim / (32 * epl) / 8), 1, 1), block 256.
+// out_kind: 1 fp16, 2 fp32, 3 shard state.
+// ---------------------------------------------------------------------------
+template <int EPL>
+__device__ __forceinline__ void combine_rows_body(
+    const float* __restrict__ partial_m, const float* __restrict__ partial_l,
+    const float* __restrict__ partial_o, void* __restrict__ output, int out_kind,
+    int rows, int max_chunks, int D)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int groups = D / (32 * EPL);                 // column groups per row
+    const int unit = blockIdx.x * 8 + warp;
+    const int row = unit / groups, col0 = (unit - row * groups) * 32 * EPL;
+    if (row >= rows) return;
+    const long long base = (long long)row * max_chunks;
+    const float m0 = (lane < max_chunks) ? partial_m[base + lane] : kNeutralM;
+    const float m1 = (lane + 32 < max_chunks) ? partial_m[base + lane + 32] : kNeutralM;
+    const float l0 = (lane < max_chunks) ? partial_l[base + lane] : 0.f;
+    const float l1 = (lane + 32 < max_chunks) ? partial_l[base + lane + 32] : 0.f;
+    float M = fmaxf(m0, m1);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float w0 = (m0 <= -1e29f) ? 0.f : __expf(m0 - M);
+    const float w1 = (m1 <= -1e29f) ? 0.f : __expf(m1 - M);
+    float L = l0 * w0 + l1 * w1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+
+    // Live splits come first (a split is empty only past the sequence's end), so the
+    // walk stops at the last split that holds anything.
+    const unsigned live0 = __ballot_sync(0xffffffffu, m0 > -1e29f), live1 = __ballot_sync(0xffffffffu, m1 > -1e29f);
+    const int n_live = live1 ? 64 - __clz(live1) : 32 - __clz(live0);
+
+    float acc[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
+    const float* op = partial_o + base * D + col0 + lane * EPL;
+    for (int c0 = 0; c0 < n_live; c0 += 8) {
+        float x[8][EPL];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;
+            if (c < n_live) {
+                const float* src = op + (long long)c * D;
+                if constexpr (EPL == 1) {
+                    x[k][0] = *src;
+                } else if constexpr (EPL == 2) {
+                    const float2 v = *reinterpret_cast<const float2*>(src);
+                    x[k][0] = v.x; x[k][1] = v.y;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < EPL; i += 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(src + i);
+                        x[k][i] = v.x; x[k][i + 1] = v.y; x[k][i + 2] = v.z; x[k][i + 3] = v.w;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) x[k][i] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;                                  // warp-uniform
+            const float w = __shfl_sync(0xffffffffu, (c < 32) ? w0 : w1, c & 31);
+            if (c < n_live && w != 0.f) {
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) acc[i] = fmaf(x[k][i], w, acc[i]);
+            }
+        }
+    }
+    if (out_kind == 3) {
+        float* st = reinterpret_cast<float*>(output) + (long long)row * (D + 2);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) st[col0 + lane * EPL + i] = acc[i];
+        if (lane == 0 && col0 == 0) { st[D] = M; st[D + 1] = L; }
+    } else {
+        const float inv = 1.f / fmaxf(L, 1e-20f);
+        if (out_kind == 2) {
+            float* o = reinterpret_cast<float*>(output) + (long long)row * D + col0 + lane * EPL;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[i] = acc[i] * inv;
+        } else {
+            __half* o = reinterpret_cast<__half*>(output) + (long long)row * D + col0 + lane * EPL;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[i] = __float2half(acc[i] * inv);
+        }
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_rows_kernel(
+    const float* __restrict__ partial_m, const float* __restrict__ partial_l,
+    const float* __restrict__ partial_o, void* __restrict__ output,
+    int num_q_heads, int head_dim, int max_chunks, int out_kind, int* __restrict__ ticket, int rows, int epl)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
+    (void)num_q_heads;
+    // epl = columns per lane; a warp covers 32 * epl columns of one row
+    if (epl == 1) combine_rows_body<1>(partial_m, partial_l, partial_o, output, out_kind, rows, max_chunks, head_dim);
+    else if (epl == 2) combine_rows_body<2>(partial_m, partial_l, partial_o, output, out_kind, rows, max_chunks, head_dim);
+    else if (epl == 4) combine_rows_body<4>(partial_m, partial_l, partial_o, output, out_kind, rows, max_chunks, head_dim);
+    else combine_rows_body<8>(partial_m, partial_l, partial_o, output, out_kind, rows, max_chunks, head_dim);
+}
+
+// ---------------------------------------------------------------------------
 // KV-range sharding across GPUs (one very long sequence): every GPU reduces its
 // own splits to ONE unnormalised state per query head, laid out as
 // [B * Hq][D + 2] floats = o[D], m, l (6,240 bytes for 12 heads of 128), the

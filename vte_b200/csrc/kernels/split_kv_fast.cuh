@@ -491,6 +491,28 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
             // ---- exchange (m, l, o) between the warps of each KV head and store the item
             const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, 2 unused
+            if (plan.wph == 1) {
+                // One warp per KV head: nothing to merge, the warp stores its own state.
+                float l_own = l_run;
+                l_own += __shfl_xor_sync(0xffffffffu, l_own, 1);
+                l_own += __shfl_xor_sync(0xffffffffu, l_own, 2);
+                const bool empty1 = (flags & kTileEmpty) != 0;
+                if (g < group) {
+                    const long long stat = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
+                                            (long long)hh * group + g) * a.max_chunks + item_c;
+                    if (!empty1 || (a.flags & kFlagWriteEmptyO)) {
+                        float* out = a.partial_o + stat * D + 2 * t;
+#pragma unroll
+                        for (int n = 0; n < NT; ++n)
+                            *reinterpret_cast<float2*>(out + n * 8) = make_float2(o_acc[n][0], o_acc[n][1]);
+                    }
+                    if (t == 0) {
+                        a.partial_m[stat] = empty1 ? kNeutralM : m_run * kLn2;
+                        a.partial_l[stat] = empty1 ? 0.f : l_own;
+                    }
+                }
+                continue;
+            }
             if (merge_pending) {
                 // everyone must have finished reading the previous item's exchange area
                 if (!mbar_wait_bounded(merge_bar0 + 8, (merge_parity >> 1) & 1u, abort_word)) {

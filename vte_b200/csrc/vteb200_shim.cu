@@ -325,6 +325,14 @@ int vteb_func_set_max_dynamic_smem(void* function, int bytes) {
                      "cuFuncSetAttribute(max dynamic shared memory)");
 }
 
+int vteb_func_set_shared_carveout(void* function, int percent) {
+    REQUIRE_INIT();
+    if (!function || percent < 0 || percent > 100) return fail(VTEB_ERR_INVALID_ARGUMENT, "bad function or percent");
+    return check_drv(g_drv.FuncSetAttribute((CUfunction)function,
+                                            CU_FUNC_ATTRIBUTE_PREFERRED_SHARED_MEMORY_CARVEOUT, percent),
+                     "cuFuncSetAttribute(shared memory carve-out)");
+}
+
 int vteb_launch(void* function, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by,
                 unsigned bz, unsigned shared_mem_bytes, void* stream, void** params, unsigned flags) {
     REQUIRE_INIT();
@@ -508,6 +516,15 @@ int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fas
     return 0;
 }
 
+int vteb_combine_rows_epl(int rows, int head_dim) {
+    int epl = head_dim / 32;
+    if (epl > 8) epl = 8;
+    if (epl < 1) epl = 1;
+    // halve the columns per lane until about two thousand warps exist
+    while (epl > 1 && (long long)rows * (head_dim / (32 * epl)) < 2048) epl /= 2;
+    return epl;
+}
+
 static int validate_attention_args(const void* q, const void* k_cache, const void* v_cache,
                                    const int* kv_offsets, void* output, int batch, int num_q_heads,
                                    int num_kv_heads, int head_dim, long long kv_batch_stride, int max_chunks) {
@@ -593,6 +610,14 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                    work + 1, (const __half*)nullptr, (const __half*)nullptr, (void*)nullptr, 0);
     if (rc) return rc;
 
+    if (max_chunks <= 64) {
+        const int rows = batch * num_q_heads;
+        const int epl = vteb_combine_rows_epl(rows, head_dim);
+        const int units = rows * (head_dim / (32 * epl));
+        return launch_rt(vteb_split_kv_combine_rows_kernel, dim3((units + 7) / 8), dim3(256), 0, s, pdl,
+                         (const float*)partial_m, (const float*)partial_l, (const float*)partial_o, output,
+                         num_q_heads, head_dim, max_chunks, out_is_f32 ? 2 : 1, work, rows, epl);
+    }
     vteb_fast_plan hp;
     vteb_split_kv_plan(num_q_heads, num_kv_heads, head_dim, &hp);
     const int dsplit = hp.combine_dsplit;
