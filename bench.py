@@ -125,7 +125,7 @@ def config_json(cfg, workload, lengths, n_layers, n_kv, splits, world, extra=Non
 
 
 # --------------------------------------------------------------------------- reference / CPU arm
-def cpu_step(layers, cfg, threads: int):
+def cpu_step(layers, threads: int):
     """One decode step of the oracle (numpy restatement of the reference's
     tools/validate_attention.py::ref_gqa_attention) over the given layers."""
     from oracle import attention_oracle as orc
@@ -151,10 +151,10 @@ def run_reference(args, rank, world):
     threads = max(1, min(os.cpu_count() or 1, sample_layers))
     bytes_step = algorithmic_bytes(cfg, lengths) * sample_layers
     for _ in range(args.warmup):
-        cpu_step(layers, cfg, threads)
+        cpu_step(layers, threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_step(layers, cfg, threads)
+        cpu_step(layers, threads)
     dt = (time.perf_counter() - t0) / args.steps
     value = bytes_step / dt / 1e12
     sample = (f"{sample_layers} of {n_layers} layers per step, every sequence of each layer, "
@@ -327,7 +327,7 @@ def run_ours(args, rank, world, local_rank):
         best = float("inf")
         for _ in range(3):
             t0 = time.perf_counter()
-            cpu_step(layers, cfg, 1)
+            cpu_step(layers, 1)
             best = min(best, time.perf_counter() - t0)
         result["cpu_baseline"] = {
             "value": bytes_step / n_layers * sample_layers / best / 1e12, "unit": UNIT, "cores": 1, "kind": "port",

@@ -1,6 +1,5 @@
 """The CPU oracle against vectors produced by the reference's own functions
 (tests/golden/make_golden.py), plus the oracle's internal consistency."""
-import hashlib
 from pathlib import Path
 
 import numpy as np

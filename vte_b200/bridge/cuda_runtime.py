@@ -21,7 +21,6 @@ import ctypes
 import logging
 import os
 import threading
-import time
 from pathlib import Path
 from typing import Optional
 

@@ -15,7 +15,6 @@ Unlike the reference's batched executor it admits ragged context lengths.
 from __future__ import annotations
 
 import ctypes
-import math
 from typing import Optional
 
 import numpy as np
@@ -101,7 +100,6 @@ class DecodeAttentionExecutor:
         self._stage_q = hip.host_alloc(self.L * self.q_bytes)
         self._stage_out = hip.host_alloc(self.L * self.out_bytes)
         self._graph_exec = None
-        self._launches = None
         self.kernel_launches_per_step = 0
 
     # ---- data movement helpers ----------------------------------------------------

@@ -16,7 +16,6 @@ from typing import Optional
 
 import numpy as np
 
-from ..bridge.errors import CudaSafetyError
 from ..bridge.memory import MemoryRegion
 from .decode_executor import DecodeAttentionExecutor
 

@@ -24,39 +24,6 @@
 
 using namespace vteb;
 
-// Optional timeline trace for kernel development (-DVTEB_TRACE): CTA 0 records
-// clock64() at a few points per tile into a global buffer.  Compiled out otherwise.
-#ifdef VTEB_TRACE
-__device__ long long vteb_trace_buf[9 * 64 * 4];
-__device__ unsigned long long vteb_trace_cta[1024 * 4];   // per CTA: %globaltimer at entry / first tile / last release / exit
-__device__ __forceinline__ unsigned long long vteb_global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define VTEB_TRACE_CTA(slot_) \
-    do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 1024) vteb_trace_cta[blockIdx.x * 4 + (slot_)] = vteb_global_ns(); } while (0)
-// per launch: [layer][kind 0 = split, 1 = combine][0 = earliest entry, 1 = latest exit, 2 = earliest "dependency resolved"]
-__device__ unsigned long long vteb_trace_launch[64 * 2 * 4];
-__device__ const void* vteb_trace_base[2];      // first layer's k_cache / output
-__device__ long long vteb_trace_stride[2];      // bytes between layers
-__device__ __forceinline__ void vteb_trace_launch_event(int kind, const void* p, int slot, bool is_max) {
-    const long long layer = ((const char*)p - (const char*)vteb_trace_base[kind]) / vteb_trace_stride[kind];
-    if (layer < 0 || layer >= 64) return;
-    unsigned long long* dst = &vteb_trace_launch[(layer * 2 + kind) * 4 + slot];
-    if (is_max) atomicMax(dst, vteb_global_ns()); else atomicMin(dst, vteb_global_ns());
-}
-#define VTEB_TRACE_LAUNCH(kind_, ptr_, slot_, is_max_) \
-    do { if ((threadIdx.x & 31) == 0) vteb_trace_launch_event(kind_, ptr_, slot_, is_max_); } while (0)
-#define VTEB_TRACE_EVENT(warp_, tile_, slot_) \
-    do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile_) < 64) \
-        vteb_trace_buf[((warp_) * 64 + (tile_)) * 4 + (slot_)] = clock64(); } while (0)
-#else
-#define VTEB_TRACE_EVENT(warp_, tile_, slot_) do {} while (0)
-#define VTEB_TRACE_CTA(slot_) do {} while (0)
-#define VTEB_TRACE_LAUNCH(kind_, ptr_, slot_, is_max_) do {} while (0)
-#endif
-
 #ifndef SPLIT_KV_CHUNK_SIZE
 #define SPLIT_KV_CHUNK_SIZE 0   // > 0 reproduces the reference's fixed chunk length
 #endif
@@ -419,14 +386,11 @@ __device__ __forceinline__ void fast_combine_kernel_body(
     int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
     extern __shared__ float combine_weight_sh[];   // [min(max_chunks, 256)]
-    VTEB_TRACE_LAUNCH(1, output, 0, false);
     grid_launch_dependents();
     grid_dependency_wait();
-    VTEB_TRACE_LAUNCH(1, output, 2, false);
     if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
     combine_slice<false>(partial_m, partial_l, partial_o, output, out_kind, head_dim, max_chunks, dsplit,
                          blockIdx.x, combine_weight_sh);
-    VTEB_TRACE_LAUNCH(1, output, 1, true);
 }
 
 extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f16_kernel(

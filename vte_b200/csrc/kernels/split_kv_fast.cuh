@@ -171,8 +171,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     if ((int)blockIdx.x < total_items) first_geom = decode_item(a, plan, blockIdx.x);
 
     if (threadIdx.x == 0) {
-        VTEB_TRACE_CTA(0);
-        VTEB_TRACE_LAUNCH(0, a.k_cache, 0, false);
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(full0 + 8 * s, 65);        // 64 asynchronous-copy arrivals + the header writer
             mbar_init(empty0 + 8 * s, plan.active_warps);
@@ -196,7 +194,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         uint32_t empty_parity = 0;
         bool dep_done = false;
         int item = blockIdx.x;
-        int trace_tile = 0;
         bool alive = true;
         while (alive) {
             const bool stop = item >= total_items;
@@ -204,7 +201,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             if (!stop && item != (int)blockIdx.x) g = decode_item(a, plan, item);
             const int ntiles = stop ? 1 : max(1, (g.end - g.start + plan.tile - 1) / plan.tile);
             for (int t = 0; t < ntiles; ++t) {
-                VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 0);
                 if (filled >= nstages) {
                     if (!mbar_wait_bounded(empty0 + 8 * stage, (empty_parity >> stage) & 1u, abort_word)) {
                         raise_abort(abort_word, a.status, kStatusEmptyTimeout);
@@ -213,7 +209,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     }
                     empty_parity ^= (1u << stage);
                 }
-                VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 1);
                 const uint32_t bar = full0 + 8 * stage;
                 const bool empty_item = !stop && g.end <= g.start;
                 const int pos0 = stop ? 0 : g.start + t * plan.tile;
@@ -247,8 +242,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 } else {
                     mbar_arrive(bar);      // no copies belong to this tile
                 }
-                VTEB_TRACE_EVENT(kLoaderWarpK, trace_tile, 2);
-                ++trace_tile;
                 ++filled;
                 stage = (stage + 1 == nstages) ? 0 : stage + 1;
             }
@@ -358,22 +351,17 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
     grid_dependency_wait();
-    if (warp == 0) VTEB_TRACE_LAUNCH(0, a.k_cache, 2, false);
     if ((int)blockIdx.x < total_items) load_q(first_geom.b, first_geom.hgroup);
 
-    int trace_tile = 0;
     for (;;) {
-        VTEB_TRACE_EVENT(warp, trace_tile, 0);
         if (!mbar_wait_bounded(full0 + 8 * stage, (full_parity >> stage) & 1u, abort_word)) {
             raise_abort(abort_word, a.status, kStatusFullTimeout);
             return;
         }
         full_parity ^= (1u << stage);
-        VTEB_TRACE_EVENT(warp, trace_tile, 1);
-        if (warp == 0 && trace_tile == 0) VTEB_TRACE_CTA(1);
         const TileHeader* hd = headers + stage;
         const int flags = hd->flags;
-        if (flags & kTileStop) { if (warp == 0) { VTEB_TRACE_CTA(3); VTEB_TRACE_LAUNCH(0, a.k_cache, 1, true); } break; }
+        if (flags & kTileStop) break;
         // Copy what is needed later: the loader may rewrite the header once every
         // consumer warp has released the stage.
         const int item_b = hd->b, item_hgroup = hd->hgroup, item_c = hd->c;
@@ -483,9 +471,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         // Hand the stage back to the loader.
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * stage);
-        VTEB_TRACE_EVENT(warp, trace_tile, 2);
-        if (warp == 0) VTEB_TRACE_CTA(2);
-        ++trace_tile;
 
         if (flags & kTileLast) {
             stage = (stage + 1 == nstages) ? 0 : stage + 1;

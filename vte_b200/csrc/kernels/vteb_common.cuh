@@ -133,26 +133,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-#ifndef VTEB_WAIT_MODE
-#define VTEB_WAIT_MODE 0
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
-#if VTEB_WAIT_MODE == 1
-    asm volatile(
-        "{\n"
-        "  .reg .pred p;\n"
-        "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-        "  selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(20000u)
-        : "memory");
-#else
     asm volatile(
         "{\n"
         "  .reg .pred p;\n"
@@ -162,10 +144,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
-#if VTEB_WAIT_MODE == 2
-    if (!done) __nanosleep(200);
-#endif
-#endif
     return done != 0;
 }
 
