@@ -214,7 +214,7 @@ def run_ours(args, rank, world, local_rank):
                                  min_chunk=None if args.min_chunk < 0 else args.min_chunk,
                                  programmatic=not args.no_pdl, compat=args.compat,
                                  prefetch_next_layer=not args.no_prefetch,
-                                 fused_combine=args.fuse)
+                                 fused_combine=args.fuse, variant=args.variant)
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
@@ -301,7 +301,7 @@ def run_ours(args, rank, world, local_rank):
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
                                    "programmatic_dependent_launch": not args.no_pdl,
                                    "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1,
-                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else "fast"}),
+                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, lite CTAs" if ex.dispatcher.lite else "fast, full CTAs")}),
             "us_per_layer_token": step_s * 1e6 / n_layers / global_cfg.batch,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
             "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
@@ -420,7 +420,8 @@ def kernel_durations(rt, ex, n_layers, reps=10):
     on the launching stream: duration = elapsed / (replays * layers), which
     includes the in-graph launch gap between consecutive kernels."""
     disp = ex.dispatcher
-    name = "flash_attention_split_kv_partial_kernel" if disp.compat else f"vteb_split_kv_partial_d{disp.head_dim}_kernel"
+    name = ("flash_attention_split_kv_partial_kernel" if disp.compat else
+            f"vteb_split_kv_partial_{'lite_' if disp.lite else ''}d{disp.head_dim}_kernel")
     out = {}
     kinds = ((0, "split_us"),) if disp.fused_combine else ((0, "split_us"), (1, "combine_us"))
     out["combine_us"] = 0.0
@@ -473,6 +474,7 @@ def main():
                     help="with N > 1: replicas (each rank its own copy, weak; default), sequences (the batch is split "
                          "over the ranks, strong), kv-range (one sequence's KV range split over the ranks, NCCL all-gather)")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--variant", default="full", choices=["full", "lite"], help="CTA shape of the split kernel")
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")

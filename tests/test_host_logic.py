@@ -49,6 +49,11 @@ def test_plan_is_pure_host_arithmetic(built_library):
         assert plan.ok == 1 and plan.hg == hg and plan.n_hgroups == nhg
         assert plan.smem_bytes <= 227 * 1024 and plan.nstages >= 2 and plan.tile % 16 == 0
         assert plan.threads == 320 and plan.combine_dsplit == d // 32
+        lite = FastPlan()
+        assert lib.vteb_split_kv_plan_lite(hq, hkv, d, ctypes.byref(lite)) == 0
+        assert lite.ok == (0 if d == 256 else 1)
+        if lite.ok:
+            assert lite.threads == 160 and lite.hg == 1 and lite.smem_bytes <= 74 * 1024 and lite.nstages >= 2
     for hq, hkv, d in [(32, 2, 128), (12, 2, 96), (12, 5, 128), (12, 0, 128)]:   # group 16, odd dim, non-divisor
         plan = FastPlan()
         assert lib.vteb_split_kv_plan(hq, hkv, d, ctypes.byref(plan)) == 0
@@ -85,9 +90,9 @@ class FakeRuntime:
     def get_num_cus(self): return self.sms
     def get_gpu_architecture(self): return "sm_100a"
     def combine_rows_epl(self, rows, d): return self._lib.vteb_combine_rows_epl(rows, d)
-    def split_kv_plan(self, hq, hkv, d):
+    def split_kv_plan(self, hq, hkv, d, lite=False):
         plan = FastPlan()
-        self._lib.vteb_split_kv_plan(hq, hkv, d, ctypes.byref(plan))
+        (self._lib.vteb_split_kv_plan_lite if lite else self._lib.vteb_split_kv_plan)(hq, hkv, d, ctypes.byref(plan))
         return plan
     def safe_malloc(self, n, tag="x"):
         p = self._next
@@ -130,7 +135,7 @@ def mapping(layer=0, stride=32768 * 2 * 128):
 # ----------------------------------------------------------------------------- dispatcher
 def test_fast_launch_list_shapes_and_signatures():
     d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, fused_combine=False)
-    assert d.enabled and not d.compat and d.max_chunks == 148
+    assert d.enabled and not d.compat and d.max_chunks == 148 and not d.lite
     launches = d.build_launches(0, mapping(), 0x7200_0000_0000, batch=1)
     assert len(launches) == 3
     (fa, aa, ga, ba, sa), (fp, ap, gp, bp, sp), (fr, ar, gr, br, sr) = launches
@@ -165,6 +170,21 @@ def test_fused_launch_list_is_append_plus_one_launch():
     d2, *_ = make_dispatcher({'attention.head_count': 12, 'attention.head_count_kv': 3, 'attention.key_length': 128},
                              fused_combine=True)
     assert not d2.fused_combine and len(d2.build_launches(0, mapping(), 0x7200_0000_0000)) == 3
+
+
+def test_lite_shape_is_opt_in():
+    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, variant="lite")
+    assert d.lite and d.max_chunks == 148
+    (_, _, _, _, _), (fp, ap, gp, bp, sp), _ = d.build_launches(0, mapping(), 0x7200_0000_0000)
+    assert gp == (296, 1, 1) and bp == (160, 1, 1) and sp <= 74 * 1024
+    assert [s for _, s in rt.loaded][1] == "vteb_split_kv_partial_lite_d128_kernel"
+    default, *_ = make_dispatcher(context_length=32768, batch_size=1)
+    assert not default.lite
+    wide, *_ = make_dispatcher({'attention.head_count': 8, 'attention.head_count_kv': 2, 'attention.key_length': 256},
+                               variant="lite")
+    assert not wide.lite                                            # no lite kernel for 256-wide heads
+    with pytest.raises(CudaSafetyError):
+        make_dispatcher(variant="tiny")
 
 
 def test_compat_launch_list_is_the_reference_geometry():

@@ -46,6 +46,7 @@ LAUNCH_PROGRAMMATIC = 1
 ATTN_COMPAT = 1
 ATTN_WRITE_EMPTY_O = 2
 ATTN_PROGRAMMATIC = 4
+ATTN_LITE = 16
 
 ERR_DEVICE_STATUS = -6
 
@@ -116,6 +117,7 @@ def _declare(lib):
         "vteb_nccl_all_reduce_max_f32": (i, [vp, vp, vp, sz, vp]),
         "vteb_nccl_comm_destroy": (i, [vp]),
         "vteb_split_kv_plan": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
+        "vteb_split_kv_plan_lite": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
         "vteb_combine_rows_epl": (i, [i, i]),
         "vteb_split_kv_decode": (i, [vp, vp, vp, vp, vp, i, vp, vp, vp, vp, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_split_kv_decode_noalloc": (i, [vp, vp, vp, vp, vp, i, i, i, i, i, f, ll, i, i, u, i, vp]),
@@ -610,10 +612,10 @@ class CudaRuntime:
         self._check_error(self._lib.vteb_stream_synchronize(self._stream), "cudaStreamSynchronize")
 
     # ------------------------------------------------------------------ attention entry points
-    def split_kv_plan(self, num_q_heads: int, num_kv_heads: int, head_dim: int) -> FastPlan:
+    def split_kv_plan(self, num_q_heads: int, num_kv_heads: int, head_dim: int, lite: bool = False) -> FastPlan:
         plan = FastPlan()
-        self._check_error(self._lib.vteb_split_kv_plan(num_q_heads, num_kv_heads, head_dim, ctypes.byref(plan)),
-                          "vteb_split_kv_plan")
+        fn = self._lib.vteb_split_kv_plan_lite if lite else self._lib.vteb_split_kv_plan
+        self._check_error(fn(num_q_heads, num_kv_heads, head_dim, ctypes.byref(plan)), "vteb_split_kv_plan")
         return plan
 
     def combine_rows_epl(self, rows: int, head_dim: int) -> int:

@@ -27,6 +27,8 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_partial_d64_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_d128_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_d256_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_lite_d64_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_lite_d128_kernel": _FAST_PARTIAL,
     "vteb_split_kv_combine_f16_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_f32_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_state_kernel": _FAST_COMBINE,

@@ -32,7 +32,7 @@ class DecodeAttentionExecutor:
                  with_append: bool = False, fixed_chunk_size=None, min_chunk: Optional[int] = None,
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
                  emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
-                 fused_combine: Optional[bool] = None):
+                 fused_combine: Optional[bool] = None, variant: str = "full"):
         self.hip = hip
         self.metadata = dict(metadata)
         self.B = int(batch_size)
@@ -74,7 +74,7 @@ class DecodeAttentionExecutor:
             hip, codegen, self.metadata, allocator=allocator, context_length=self.S, batch_size=self.B,
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
-            prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine)
+            prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant)
 
         A = allocator.allocate
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]

@@ -58,33 +58,55 @@ __device__ __forceinline__ void raise_abort(volatile int* abort_word, int* statu
     }
 }
 
-// Copies `nrows` (a multiple of 8) position rows of `row_bytes` <= 1024 bytes each
-// (this lane's 16-byte pieces of them) from global to padded shared rows; rows at
-// or past `nvalid` are taken from `src_last`.  `src`, `src_last` and `dst` already
-// include the lane's 16-byte offset.  Eight rows' addresses are formed first and
-// their copies issued back to back: an asynchronous copy holds its address
-// registers until the load/store unit has picked it up, so a loop that bumps one
-// pointer per copy stalls for that latency on every row (measured: ~230 cycles
-// per row instead of ~16).
+// Copies `nrows` (a multiple of 16) position rows of `row_bytes` <= 1024 bytes each from
+// global to padded shared rows with 16-byte asynchronous copies; rows at or past `nvalid`
+// are taken from `src_last` (the item's last row).  A warp instruction moves 512 bytes:
+// one piece of a long row, or several whole short rows (256-byte rows: two per
+// instruction).  Eight instructions' addresses are formed first and their copies issued
+// back to back: an asynchronous copy holds its address registers until the load/store
+// unit has picked it up, so a loop that bumps one pointer per copy stalls for that
+// latency on every row (measured: ~230 cycles per row instead of ~16).
 __device__ __forceinline__ void copy_rows_async(const unsigned char* src, const unsigned char* src_last,
                                                 uint32_t dst, int nrows, int nvalid, int row_bytes,
                                                 int row_pitch, long long pos_stride, int lane) {
-    const bool piece0 = lane * 16 < row_bytes;                    // bytes [0, 512) of the row
-    const bool piece1 = 512 + lane * 16 < row_bytes;              // bytes [512, 1024)
-    for (int r0 = 0; r0 < nrows; r0 += 8) {
-        const unsigned char* s[8];
+    if (row_bytes >= 512) {
+        const bool piece0 = lane * 16 < row_bytes;                    // bytes [0, 512) of the row
+        const bool piece1 = 512 + lane * 16 < row_bytes;              // bytes [512, 1024)
+        src += lane * 16; src_last += lane * 16; dst += lane * 16;
+        for (int r0 = 0; r0 < nrows; r0 += 8) {
+            const unsigned char* s[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s[i] = (r0 + i < nvalid) ? src + (long long)i * pos_stride : src_last;
-        if (piece0) {
+            for (int i = 0; i < 8; ++i) s[i] = (r0 + i < nvalid) ? src + (long long)i * pos_stride : src_last;
+            if (piece0) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch, s[i]);
+                for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch, s[i]);
+            }
+            if (piece1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch + 512, s[i] + 512);
+            }
+            src += 8 * pos_stride;
+            dst += 8 * row_pitch;
         }
-        if (piece1) {
+    } else {
+        const int lanes_per_row = row_bytes >> 4;                     // 16 for 256-byte rows, 8 for 128
+        const int rows_per_instr = 32 / lanes_per_row;
+        const int my_row = lane / lanes_per_row, my_col = (lane - my_row * lanes_per_row) * 16;
+        src += my_col; src_last += my_col;
+        for (int r0 = 0; r0 < nrows; r0 += 8 * rows_per_instr) {
+            const unsigned char* s[8];
+            uint32_t d[8];
+            bool on[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch + 512, s[i] + 512);
+            for (int i = 0; i < 8; ++i) {
+                const int r = r0 + i * rows_per_instr + my_row;
+                on[i] = r < nrows && my_row < rows_per_instr;
+                s[i] = (r < nvalid) ? src + (long long)r * pos_stride : src_last;
+                d[i] = dst + r * row_pitch + my_col;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) if (on[i]) async_copy_16(d[i], s[i]);
         }
-        src += 8 * pos_stride;
-        dst += 8 * row_pitch;
     }
 }
 
@@ -144,11 +166,14 @@ __device__ __forceinline__ ItemGeometry decode_item(const FastArgs& a, const Fas
     return g;
 }
 
-template <int D>
+template <int D, int CW>
 __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 {
+    constexpr bool kLite = (CW == kLiteConsumerWarps);
+    constexpr int kLoaderWarpK = CW;          // loads K rows (and V rows in the lite shape), owns the work queue
+    constexpr int kLoaderWarpV = CW + 1;      // full shape only: loads V rows, follows the K loader's headers
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const FastPlan plan = make_fast_plan(a.num_q_heads, a.num_kv_heads, D);
+    const FastPlan plan = make_fast_plan(a.num_q_heads, a.num_kv_heads, D, kLite ? 1 : 0);
     const int group = a.num_q_heads / a.num_kv_heads;
 
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem_raw + kAbortOffset);
@@ -172,7 +197,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(full0 + 8 * s, 65);        // 64 asynchronous-copy arrivals + the header writer
+            mbar_init(full0 + 8 * s, kLite ? 33 : 65);   // asynchronous-copy arrivals of the loader lanes + the header writer
             mbar_init(empty0 + 8 * s, plan.active_warps);
             mbar_init(hdr0 + 8 * s, 1);
         }
@@ -234,10 +259,16 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     const int nrows = vteb_round_up(nvalid, kBlockPos);
                     const unsigned char* src = reinterpret_cast<const unsigned char*>(a.k_cache) +
                         2ll * ((long long)g.b * a.kv_batch_stride + (long long)g.hgroup * plan.hg * D) +
-                        (long long)pos0 * pos_stride + lane * 16;
+                        (long long)pos0 * pos_stride;
                     const unsigned char* src_last = src + (long long)(g.end - 1 - pos0) * pos_stride;
-                    const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + lane * 16;
+                    const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes);
                     copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
+                    if constexpr (kLite) {
+                        const long long k_to_v = reinterpret_cast<const unsigned char*>(a.v_cache) -
+                                                 reinterpret_cast<const unsigned char*>(a.k_cache);
+                        copy_rows_async(src + k_to_v, src_last + k_to_v, dst + plan.tile * plan.row_pitch, nrows, nvalid,
+                                        plan.row_bytes, plan.row_pitch, pos_stride, lane);
+                    }
                     async_copy_arrive(bar);
                 } else {
                     mbar_arrive(bar);      // no copies belong to this tile
@@ -260,13 +291,18 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                       2ll * (long long)g.b * a.kv_batch_stride + (long long)g.start * pos_stride,
                                   (long long)(g.end - g.start) * pos_stride, lane);
         }
+        if (kLite && a.next_v_cache != nullptr && plan.n_hgroups == 1 && total_items <= (int)gridDim.x &&
+            (int)blockIdx.x < total_items && first_geom.end > first_geom.start)
+            prefetch_range_l2(reinterpret_cast<const unsigned char*>(a.next_v_cache) +
+                                  2ll * (long long)first_geom.b * a.kv_batch_stride + (long long)first_geom.start * pos_stride,
+                              (long long)(first_geom.end - first_geom.start) * pos_stride, lane);
         if (!dep_done) grid_dependency_wait();
         asm volatile("cp.async.wait_all;" ::: "memory");   // own copies have landed before the warp leaves
         return;
     }
 
-    // ===================================================================== V loader
-    if (warp == kLoaderWarpV) {
+    // ===================================================================== V loader (full shape)
+    if (!kLite && warp == kLoaderWarpV) {
         int stage = 0;
         uint32_t hdr_parity = 0;
         bool dep_done = false;
@@ -283,9 +319,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 const int nrows = vteb_round_up(hd.nvalid, kBlockPos);
                 const unsigned char* src = reinterpret_cast<const unsigned char*>(a.v_cache) +
                     2ll * ((long long)hd.b * a.kv_batch_stride + (long long)hd.hgroup * plan.hg * D) +
-                    (long long)hd.pos0 * pos_stride + lane * 16;
+                    (long long)hd.pos0 * pos_stride;
                 const unsigned char* src_last = src + (long long)(hd.last_pos - hd.pos0) * pos_stride;
-                const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_pitch + lane * 16;
+                const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_pitch;
                 copy_rows_async(src, src_last, dst, nrows, hd.nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
                 async_copy_arrive(bar);
             } else {
@@ -536,10 +572,10 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 const size_t wstride = (size_t)plan.hg * group * pitch;                  // next warp of the same head
                 constexpr int NV = (D + 127) / 128;                                      // float4 columns per lane
                 const bool col_ok = (D >= 128) || lane < D / 4;
-                float mw[kConsumerWarps], lw[kConsumerWarps];
-                float4 ow[kConsumerWarps][NV];
+                float mw[CW], lw[CW];
+                float4 ow[CW][NV];
 #pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) {
+                for (int w = 0; w < CW; ++w) {
                     const bool on = w < plan.wph;
                     const float* src = src0 + (on ? w : 0) * wstride;
                     mw[w] = on ? src[D + 4] : kNeutralM;
@@ -551,13 +587,13 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 }
                 float mm = kNeutralM;
 #pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) mm = fmaxf(mm, mw[w]);
+                for (int w = 0; w < CW; ++w) mm = fmaxf(mm, mw[w]);
                 float ll = 0.f;
                 float4 acc[NV];
 #pragma unroll
                 for (int i = 0; i < NV; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) {
+                for (int w = 0; w < CW; ++w) {
                     const float wt = fast_exp2(mw[w] - mm);       // absent warps: exp2(-1e30 - mm) = 0 (or 1 * zeros)
                     ll = fmaf(lw[w], wt, ll);
 #pragma unroll
@@ -585,7 +621,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
     }
 
-    if (a.out_kind == 0) return;
+    if (kLite || a.out_kind == 0) return;
     // ===================================================================== in-launch combine
     // (needs all eight consumer warps; the host only asks for it then)
     // 1. every consumer warp's partial stores are fenced, then counted on a CTA barrier
@@ -614,8 +650,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         combine_slice<true>(a.partial_m, a.partial_l, a.partial_o, a.output, a.out_kind, D, a.max_chunks, dsplit, slice, merge);
 }
 
-#define VTEB_FAST_PARTIAL(NAME, DIM)                                                                  \
-    extern "C" __global__ void __launch_bounds__(kFastThreads, 1) NAME(                               \
+#define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, THREADS, CTAS_PER_SM)                                    \
+    extern "C" __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) NAME(                          \
         const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
         const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
         float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
@@ -635,9 +671,11 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
         a.output = output; a.out_kind = out_kind;                                                     \
         (void)head_dim;                                                                               \
-        fast_partial_body<DIM>(a);                                                                    \
+        fast_partial_body<DIM, CWARPS>(a);                                                            \
     }
 
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64, kFullConsumerWarps, kFullThreads, 1)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128, kFullConsumerWarps, kFullThreads, 1)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256, kFullConsumerWarps, kFullThreads, 1)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_lite_d64_kernel, 64, kLiteConsumerWarps, kLiteThreads, kLiteCtasPerSm)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_lite_d128_kernel, 128, kLiteConsumerWarps, kLiteThreads, kLiteCtasPerSm)

@@ -9,10 +9,18 @@
 
 namespace vteb {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kLoaderWarpK = kConsumerWarps;             // loads K rows, owns the work queue
-constexpr int kLoaderWarpV = kConsumerWarps + 1;         // loads V rows, follows the K loader's headers
-constexpr int kFastThreads = (kConsumerWarps + 2) * 32;  // 320
+// Two shapes of the split kernel's CTA:
+//   full: 8 consumer warps + 2 loader warps (K rows / V rows), one CTA per SM, for work
+//         that keeps an SM busy for tens of microseconds;
+//   lite: 4 consumer warps + 1 loader warp, one KV head per work item, small enough that
+//         three CTAs share an SM, so that under programmatic dependent launch the next
+//         layer's CTAs are already resident and loading while this layer finishes.
+constexpr int kFullConsumerWarps = 8;
+constexpr int kLiteConsumerWarps = 4;
+constexpr int kFullThreads = (kFullConsumerWarps + 2) * 32;   // 320
+constexpr int kLiteThreads = (kLiteConsumerWarps + 1) * 32;   // 160
+constexpr int kLiteCtasPerSm = 3;
+constexpr int kLiteSmemBudget = 74 * 1024;                    // per CTA, three per SM
 constexpr int kMaxStages = 8;
 constexpr int kBlockPos = 16;                            // positions per mma step
 constexpr float kLog2e = 1.4426950408889634f;
@@ -61,6 +69,9 @@ struct FastPlan {
     int stage_bytes;   // K tile + V tile
     int merge_bytes;   // per-warp (m, l, o) exchange area
     int q_bytes;       // Q operand fragments in shared memory (keeps them out of registers)
+    int consumer_warps;
+    int loader_warps;
+    int threads;
     int nstages;
     int smem_bytes;    // total dynamic shared memory
     int ok;            // 0 when the geometry is outside what the fast kernel covers
@@ -71,34 +82,39 @@ constexpr int kMergePad = 8;       // floats after o[D] in an exchange row: 4 un
 
 __host__ __device__ inline int vteb_round_up(int x, int m) { return (x + m - 1) / m * m; }
 
-__host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim) {
+__host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim, int lite = 0) {
     FastPlan p;
     p.ok = 0;
     p.hg = p.n_hgroups = p.wph = p.active_warps = p.tile = p.row_bytes = p.row_pitch = 0;
     p.stage_bytes = p.merge_bytes = p.q_bytes = p.nstages = p.smem_bytes = 0;
+    const int cw = lite ? kLiteConsumerWarps : kFullConsumerWarps;
+    p.consumer_warps = cw;
+    p.loader_warps = lite ? 1 : 2;
+    p.threads = (cw + p.loader_warps) * 32;
     if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0) return p;
     int group = num_q_heads / num_kv_heads;
     if (group > 8) return p;
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return p;
-    // Largest divisor of num_kv_heads with hg * head_dim <= 512 halves and hg <= 8.
-    int cap = 512 / head_dim;
-    if (cap > kConsumerWarps) cap = kConsumerWarps;
+    // full: largest divisor of num_kv_heads with hg * head_dim <= 512 halves and hg <= 8;
+    // lite: one KV head per item.
+    int cap = lite ? 1 : 512 / head_dim;
+    if (cap > cw) cap = cw;
     int hg = 1;
     for (int d = 1; d <= cap; ++d) if (num_kv_heads % d == 0) hg = d;
     p.hg = hg;
     p.n_hgroups = num_kv_heads / hg;
-    p.wph = kConsumerWarps / hg;
+    p.wph = cw / hg;
     p.active_warps = p.wph * hg;
     p.row_bytes = hg * head_dim * 2;
     p.row_pitch = p.row_bytes + 16;
-    int tile = (16384 / p.row_bytes) / kBlockPos * kBlockPos;
+    int tile = ((lite ? 8192 : 16384) / p.row_bytes) / kBlockPos * kBlockPos;
     if (tile < kBlockPos) tile = kBlockPos;
     if (tile > 64) tile = 64;
     p.tile = tile;
     p.stage_bytes = vteb_round_up(2 * tile * p.row_pitch, 128);
     p.merge_bytes = vteb_round_up(p.active_warps * group * (head_dim + kMergePad) * 4, 128);
     p.q_bytes = hg * (head_dim / 8) * 32 * 4;   // one fragment image per KV head, shared by its warps
-    int left = kSmemBudget - kCtrlBytes - p.merge_bytes - p.q_bytes;
+    int left = (lite ? kLiteSmemBudget : kSmemBudget) - kCtrlBytes - p.merge_bytes - p.q_bytes;
     int n = left / p.stage_bytes;
     if (n > kMaxStages) n = kMaxStages;
     if (n < 2) return p;

@@ -131,7 +131,7 @@ int check_nccl(int r, const char* what) {
 
 // Per-process record of which in-library kernels already had their dynamic
 // shared memory limit raised.
-bool g_fast_attr_set[3] = {false, false, false};
+bool g_fast_attr_set[5] = {false, false, false, false, false};
 
 template <typename... Args>
 int launch_rt(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -500,9 +500,9 @@ int vteb_nccl_comm_destroy(void* comm) {
 }
 
 // ---- split-KV decode attention ---------------------------------------------
-int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan) {
+static int fill_plan(int num_q_heads, int num_kv_heads, int head_dim, int lite, vteb_fast_plan* plan) {
     if (!plan) return fail(VTEB_ERR_INVALID_ARGUMENT, "null plan");
-    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim);
+    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, lite);
     memset(plan, 0, sizeof(*plan));
     plan->ok = p.ok;
     plan->hg = p.hg;
@@ -510,10 +510,20 @@ int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fas
     plan->tile = p.tile;
     plan->nstages = p.nstages;
     plan->smem_bytes = p.smem_bytes;
-    plan->threads = vteb::kFastThreads;
+    plan->threads = p.threads;
     plan->combine_dsplit = head_dim >= 32 ? head_dim / 32 : 1;   // one CTA per 32 output columns
     plan->combine_smem_bytes = 4;
     return 0;
+}
+
+int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan) {
+    return fill_plan(num_q_heads, num_kv_heads, head_dim, 0, plan);
+}
+
+int vteb_split_kv_plan_lite(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan) {
+    int rc = fill_plan(num_q_heads, num_kv_heads, head_dim, 1, plan);
+    if (rc == 0 && head_dim == 256) plan->ok = 0;   // no lite kernel is built for 256-wide heads
+    return rc;
 }
 
 int vteb_combine_rows_epl(int rows, int head_dim) {
@@ -578,7 +588,8 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                          (const float*)partial_o, (__half*)output, num_q_heads, head_dim, max_chunks);
     }
 
-    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim);
+    const bool lite = (flags & VTEB_ATTN_LITE) != 0 && head_dim != 256;
+    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, lite ? 1 : 0);
     if (!p.ok)
         return fail(VTEB_ERR_UNSUPPORTED, "fast split kernel does not cover Hq=%d Hkv=%d D=%d; pass VTEB_ATTN_COMPAT",
                     num_q_heads, num_kv_heads, head_dim);
@@ -587,7 +598,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     if (n_ctas <= 0) {
         int sms = 0;
         if ((rc = check_rt(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g_device), "sm count"))) return rc;
-        n_ctas = sms;
+        n_ctas = lite ? sms * vteb::kLiteCtasPerSm : sms;
     }
     if (n_ctas > items) n_ctas = (int)items;
 
@@ -595,7 +606,9 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                                int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*, const __half*, void*, int);
     FastKernel fk;
     int slot;
-    if (head_dim == 64) { fk = vteb_split_kv_partial_d64_kernel; slot = 0; }
+    if (lite && head_dim == 64) { fk = vteb_split_kv_partial_lite_d64_kernel; slot = 3; }
+    else if (lite) { fk = vteb_split_kv_partial_lite_d128_kernel; slot = 4; }
+    else if (head_dim == 64) { fk = vteb_split_kv_partial_d64_kernel; slot = 0; }
     else if (head_dim == 128) { fk = vteb_split_kv_partial_d128_kernel; slot = 1; }
     else { fk = vteb_split_kv_partial_d256_kernel; slot = 2; }
     if (!g_fast_attr_set[slot]) {
@@ -604,7 +617,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
         g_fast_attr_set[slot] = true;
     }
     const int kflags = (flags & VTEB_ATTN_WRITE_EMPTY_O) ? kFlagWriteEmptyO : 0;
-    rc = launch_rt(fk, dim3(n_ctas), dim3(vteb::kFastThreads), (size_t)p.smem_bytes, s, pdl, qh, kh, vh,
+    rc = launch_rt(fk, dim3(n_ctas), dim3(p.threads), (size_t)p.smem_bytes, s, pdl, qh, kh, vh,
                    partial_m, partial_l, partial_o, num_q_heads, num_kv_heads, head_dim, scale, kv_offsets,
                    (int)kv_batch_stride, max_chunks, batch, min_chunk, kflags, (const int*)nullptr, work,
                    work + 1, (const __half*)nullptr, (const __half*)nullptr, (void*)nullptr, 0);
