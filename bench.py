@@ -107,6 +107,18 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def balanced_assignment(lengths, world):
+    """Longest-first onto the least loaded rank, every rank getting batch / world sequences."""
+    per_rank = len(lengths) // world
+    load = [0] * world
+    picked = [[] for _ in range(world)]
+    for b in np.argsort(-lengths.astype(np.int64), kind="stable"):
+        r = min((r for r in range(world) if len(picked[r]) < per_rank), key=lambda r: load[r])
+        picked[r].append(int(b))
+        load[r] += int(lengths[b])
+    return [np.array(sorted(p), dtype=np.int64) for p in picked]
+
+
 def metadata(cfg):
     return {'attention.head_count': cfg.num_q_heads, 'attention.head_count_kv': cfg.num_kv_heads,
             'attention.key_length': cfg.head_dim}
@@ -200,8 +212,12 @@ def run_ours(args, rank, world, local_rank):
         first, last = sequences_of_rank(cfg.batch, rank, world)
         if last <= first:
             raise SystemExit(f"rank {rank} got no sequence: batch {cfg.batch} over {world} ranks")
-        lengths = lengths[first:last]
-        cfg = replace(cfg, batch=last - first)
+        if args.balance and cfg.batch % world == 0:
+            mine = balanced_assignment(lengths, world)[rank]
+            lengths = lengths[mine]
+        else:
+            lengths = lengths[first:last]
+        cfg = replace(cfg, batch=len(lengths))
     rt = CudaRuntime(device_index=local_rank)
     rt.initialize()
     free_b, total_b = rt.get_real_mem_info()
@@ -356,9 +372,9 @@ def run_kv_range(args, rank, world, local_rank, rdzv, cfg, n_layers):
     lo, hi = kv_range_of_rank(total, rank, world)
     rt = CudaRuntime(device_index=local_rank)
     rt.initialize()
-    comm = NcclCommunicator(rt, rank, world, rdzv)
+    comm = NcclCommunicator(rt, rank, world, rdzv) if args.exchange == "nccl" else None
     sh = KVRangeShardedDecode(rt, CodegenEngine(), metadata(cfg), hi - lo, n_layers, comm, num_splits=args.splits or None,
-                              programmatic=not args.no_pdl)
+                              programmatic=not args.no_pdl, exchange=args.exchange, rendezvous=rdzv)
     for l in range(n_layers):
         sh.ex.fill_cache_on_device(l, cfg.base_seed * 1000 + l * world + rank, cfg.sigma_kv)
         rng = np.random.default_rng([cfg.base_seed, l, 99])
@@ -393,8 +409,9 @@ def run_kv_range(args, rank, world, local_rank, rdzv, cfg, n_layers):
                 "warmup": max(3, args.warmup), "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
                 "config": config_json(cfg, args.workload, lengths, n_layers, n_layers, sh.ex.dispatcher.max_chunks, world,
-                                      {"partition": f"KV range split over {world} GPUs, NCCL all-gather of "
-                                                    f"{sh.state_floats * 4} bytes per rank per layer",
+                                      {"partition": f"KV range split over {world} GPUs, "
+                                                    + ("NCCL all-gather" if args.exchange == "nccl" else "peer stores over NVLink")
+                                                    + f" of {sh.state_floats * 4} bytes per rank per layer",
                                        "input_generation": "device fill (counter-based normal)"}),
                 "us_per_layer_token": step_s * 1e6 / n_layers,
                 "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
@@ -405,7 +422,8 @@ def run_kv_range(args, rank, world, local_rank, rdzv, cfg, n_layers):
                 "parity": {"finite": finite, "note": "parity of this path is asserted by the tests"}}
         print(json.dumps(line), flush=True)
     sh.cleanup()
-    comm.destroy()
+    if comm is not None:
+        comm.destroy()
     rt.cleanup()
     rdzv.barrier()
     rdzv.close()
@@ -473,6 +491,10 @@ def main():
     ap.add_argument("--partition", default="", choices=["", "replicas", "sequences", "kv-range"],
                     help="with N > 1: replicas (each rank its own copy, weak; default), sequences (the batch is split "
                          "over the ranks, strong), kv-range (one sequence's KV range split over the ranks, NCCL all-gather)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="kv-range partition: how the states travel")
+    ap.add_argument("--balance", action="store_true",
+                    help="sequences partition: give each rank the same number of sequences but pick them "
+                         "longest-first onto the least loaded rank instead of contiguous blocks")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--variant", default="full", choices=["full", "lite"], help="CTA shape of the split kernel")
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")

@@ -123,6 +123,15 @@ int vteb_nccl_all_gather_f32(void* comm, const void* send, void* recv, size_t co
 int vteb_nccl_all_reduce_max_f32(void* comm, const void* send, void* recv, size_t count, void* stream);
 int vteb_nccl_comm_destroy(void* comm);
 
+/* ---- peer memory between the ranks of one node (no counterpart in the reference) ---
+ * cudaIpcGetMemHandle / cudaIpcOpenMemHandle: a rank exports a whole cudaMalloc
+ * allocation (64-byte handle, sent through the host rendezvous) and its peers map it;
+ * kernels then store into it over NVLink.  Used by the KV-range sharded path to
+ * exchange the (o, m, l) states without a collective library. */
+int vteb_ipc_get_handle(void* dev_ptr, void* handle64);
+int vteb_ipc_open_handle(const void* handle64, void** dev_ptr);
+int vteb_ipc_close_handle(void* dev_ptr);
+
 /* ---- split-KV decode attention, direct launchers -------------------------
  * These launch the same kernels the cubin exports, from inside the library.
  *

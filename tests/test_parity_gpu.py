@@ -298,8 +298,10 @@ def test_kv_range_shards_merge_to_the_full_result(cuda_runtime, codegen):
         sh.cleanup()
 
 
-def test_two_gpu_kv_range_sharding_over_nccl(cuda_runtime):
-    """Two ranks, one process per GPU, NCCL all-gather of the shard states.
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_two_gpu_kv_range_sharding(cuda_runtime, exchange):
+    """Two ranks, one process per GPU; the shard states travel by NCCL all-gather or by
+    peer stores into exported boards.
     Needs two devices; on a one-GPU box the multi-rank logic is covered by the
     gloo tests and the single-GPU shard test above."""
     import subprocess, sys, os, socket
@@ -312,7 +314,7 @@ def test_two_gpu_kv_range_sharding_over_nccl(cuda_runtime):
     procs = []
     for r in range(2):
         env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", VTEB_TEST_EXCHANGE=exchange)
         procs.append(subprocess.Popen([sys.executable, str(Path(__file__).parent / "multirank_workers.py")], env=env,
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=240)[0] for p in procs]

@@ -116,6 +116,9 @@ def _declare(lib):
         "vteb_nccl_all_gather_f32": (i, [vp, vp, vp, sz, vp]),
         "vteb_nccl_all_reduce_max_f32": (i, [vp, vp, vp, sz, vp]),
         "vteb_nccl_comm_destroy": (i, [vp]),
+        "vteb_ipc_get_handle": (i, [vp, vp]),
+        "vteb_ipc_open_handle": (i, [vp, vpp]),
+        "vteb_ipc_close_handle": (i, [vp]),
         "vteb_split_kv_plan": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
         "vteb_split_kv_plan_lite": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
         "vteb_combine_rows_epl": (i, [i, i]),
@@ -610,6 +613,30 @@ class CudaRuntime:
     def stream_synchronize(self):
         self._require_init()
         self._check_error(self._lib.vteb_stream_synchronize(self._stream), "cudaStreamSynchronize")
+
+    # ------------------------------------------------------------------ peer memory
+    def ipc_export(self, ptr) -> bytes:
+        """64-byte handle of the cudaMalloc allocation that starts at `ptr`."""
+        self._require_init()
+        val = _ptr_value(ptr)
+        if val not in self._active_allocations:
+            raise CudaSafetyError("only the base of a tracked allocation can be exported to peers")
+        buf = ctypes.create_string_buffer(64)
+        self._check_error(self._lib.vteb_ipc_get_handle(ctypes.c_void_p(val), buf), "cudaIpcGetMemHandle")
+        return buf.raw
+
+    def ipc_open(self, handle: bytes) -> int:
+        """Map a peer rank's exported allocation; returns its address in this process."""
+        self._require_init()
+        if len(handle) != 64:
+            raise CudaSafetyError(f"ipc handle has {len(handle)} bytes, expected 64")
+        p = ctypes.c_void_p()
+        self._check_error(self._lib.vteb_ipc_open_handle(ctypes.create_string_buffer(handle, 64), ctypes.byref(p)),
+                          "cudaIpcOpenMemHandle")
+        return p.value
+
+    def ipc_close(self, ptr) -> None:
+        self._check_error(self._lib.vteb_ipc_close_handle(ctypes.c_void_p(_ptr_value(ptr))), "cudaIpcCloseMemHandle")
 
     # ------------------------------------------------------------------ attention entry points
     def split_kv_plan(self, num_q_heads: int, num_kv_heads: int, head_dim: int, lite: bool = False) -> FastPlan:

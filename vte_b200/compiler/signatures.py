@@ -34,6 +34,9 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_combine_state_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_rows_kernel": [P, P, P, P, I, I, I, I, P, I, I],
     "vteb_merge_shard_states_kernel": [P, P, I, I, I],
+    "vteb_push_shard_state_kernel": [P, ctypes.Structure, I, I, I, I, I, P],
+    "vteb_merge_shard_states_p2p_kernel": [P, P, P, I, I, I, I, I, P, P],
+    "vteb_advance_step_kernel": [P],
 }
 
 # template name (what the reference passes to load_kernel_safe) -> source file

@@ -34,11 +34,31 @@ def sequences_of_rank(batch: int, rank: int, world: int) -> tuple[int, int]:
     return kv_range_of_rank(batch, rank, world)
 
 
+class PeerTable(ctypes.Structure):
+    """Kernel argument of vteb_push_shard_state_kernel: every rank's board and flag array
+    as mapped into this process (own rank: the local allocation)."""
+    _fields_ = [("board", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8)]
+
+
 class KVRangeShardedDecode:
+    """`exchange="nccl"`: ncclAllGather of the states.  `exchange="p2p"`: every rank stores
+    its state into each peer's exported board over NVLink and the merge kernel waits
+    (bounded) for the peers' flags; needs `rendezvous` to swap the memory handles, at most
+    eight ranks, one process per GPU on one node."""
+
     def __init__(self, hip, codegen, metadata: dict, shard_context_length: int, n_layers: int, comm, *,
-                 n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, programmatic: Optional[bool] = None):
+                 n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, programmatic: Optional[bool] = None,
+                 exchange: str = "nccl", rendezvous=None):
         self.hip, self.comm = hip, comm
-        self.world = comm.world if comm is not None else 1
+        self.world = comm.world if comm is not None else (rendezvous.world if rendezvous is not None else 1)
+        self.rank = comm.rank if comm is not None else (rendezvous.rank if rendezvous is not None else 0)
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError(f"exchange must be nccl or p2p, not {exchange!r}")
+        if exchange == "p2p" and (rendezvous is None or self.world > 8):
+            raise ValueError("the p2p exchange needs the host rendezvous and at most eight ranks")
+        self.exchange, self.rdzv = exchange, rendezvous
+        self._peer_ptrs: list[int] = []
+        self._board = None
         self.L = int(n_layers)
         self.ex = DecodeAttentionExecutor(hip, codegen, metadata, 1, shard_context_length, n_layers,
                                           n_kv_buffers=n_kv_buffers, num_splits=num_splits, emit_state=True,
@@ -52,12 +72,42 @@ class KVRangeShardedDecode:
         arch = hip.get_gpu_architecture()
         _, self._merge_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_kernel')
         self._stage_merged = hip.host_alloc(self.L * self.rows * ex.D * 4)
+        if self.exchange == "p2p" and self.world > 1:
+            self._setup_peer_boards(codegen, arch)
+
+    def _setup_peer_boards(self, codegen, arch):
+        """One allocation per rank: board floats, then flags, then the step word; exported to
+        the peers through the host rendezvous."""
+        hip = self.hip
+        self._board_floats = 2 * self.L * self.world * self.state_floats
+        self._flag_ints = 2 * self.L * self.world
+        nbytes = self._board_floats * 4 + self._flag_ints * 4 + 64
+        self._board = hip.safe_malloc(nbytes, "shard_states.board")
+        hip.safe_memset(self._board, nbytes, "shard_states.board")
+        hip.synchronize()
+        handles = self.rdzv.allgather(hip.ipc_export(self._board))
+        table = PeerTable()
+        for r in range(self.world):
+            base = self._board.value if r == self.rank else hip.ipc_open(handles[r])
+            if r != self.rank:
+                self._peer_ptrs.append(base)
+            table.board[r] = base
+            table.flags[r] = base + self._board_floats * 4
+        self._peers = table
+        self._flags_ptr = self._board.value + self._board_floats * 4
+        self._step_ptr = self._flags_ptr + self._flag_ints * 4
+        _, self._push_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_push_shard_state_kernel')
+        _, self._merge_p2p_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_p2p_kernel')
+        _, self._advance_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_advance_step_kernel')
+        self.rdzv.barrier()          # every board is zeroed and mapped before anyone pushes
 
     def _after_layer(self, l: int) -> int:
         """Recorded right after layer l's split + state-combine launches: all-gather, merge."""
         ex = self.ex
         state_ptr = ex.out_all.ptr + l * ex.out_bytes
         gathered_ptr = self.gathered.ptr + l * self.world * self.state_floats * 4
+        if self.world > 1 and self.exchange == "p2p":
+            return self._after_layer_p2p(l, state_ptr)
         if self.world > 1:
             self.comm.all_gather_f32(state_ptr, gathered_ptr, self.state_floats)
         else:
@@ -71,6 +121,28 @@ class KVRangeShardedDecode:
         finally:
             self.hip.programmatic_launch = pdl
         return 2 if self.world > 1 else 1
+
+    def _after_layer_p2p(self, l: int, state_ptr: int) -> int:
+        ex, hip = self.ex, self.hip
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        pdl = hip.programmatic_launch
+        hip.programmatic_launch = False
+        try:
+            hip.launch_kernel_recorded(self._push_fn, [vp(state_ptr), self._peers, ci(self.world), ci(self.rank), ci(l),
+                                                       ci(self.L), ci(self.state_floats), vp(self._step_ptr)],
+                                       (self.world, 1, 1), (256, 1, 1), 0)
+            hip.launch_kernel_recorded(self._merge_p2p_fn,
+                                       [vp(self._board.value), vp(self._flags_ptr), vp(self.merged.ptr + l * self.rows * ex.D * 4),
+                                        ci(self.world), ci(self.rows), ci(ex.D), ci(l), ci(self.L), vp(self._step_ptr),
+                                        vp(ex.dispatcher.work_ptr + 4)],
+                                       (self.rows, 1, 1), (ex.D, 1, 1), 0)
+            n = 2
+            if l == self.L - 1:
+                hip.launch_kernel_recorded(self._advance_fn, [vp(self._step_ptr)], (1, 1, 1), (32, 1, 1), 0)
+                n += 1
+        finally:
+            hip.programmatic_launch = pdl
+        return n
 
     def execute_decode(self, local_kv_offset: int) -> np.ndarray:
         """One decode step; returns the merged attention output [L, Hq, D] fp32
@@ -91,6 +163,14 @@ class KVRangeShardedDecode:
         self.ex.launch_step()
 
     def cleanup(self):
+        if self._board is not None:
+            self.hip.synchronize()
+            self.rdzv.barrier()      # nobody is still storing into a peer's board
+            for p in self._peer_ptrs:
+                self.hip.ipc_close(p)
+            self._peer_ptrs = []
+            self.hip.safe_free(self._board, "shard_states.board")
+            self._board = None
         if self._stage_merged is not None and self._stage_merged.value:
             self.hip.host_free(self._stage_merged)
             self._stage_merged = None

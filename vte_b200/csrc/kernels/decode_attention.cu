@@ -560,4 +560,92 @@ extern "C" __global__ void vteb_merge_shard_states_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same exchange without a collective library: every rank stores its state
+// row block straight into each peer's "board" over NVLink (plain peer stores into
+// memory the peer exported), then raises a flag there; the merge kernel waits,
+// bounded, for the flags of all ranks.  Boards are double-buffered by step parity
+// (a rank can run at most one step ahead of the slowest: its next merge needs that
+// rank's push), flags hold step + 1, and the step word is advanced by the last
+// kernel of the step.
+//   board: [2 parities][n_layers][world][state_floats] floats
+//   flags: [2 parities][n_layers][world] ints
+// ---------------------------------------------------------------------------
+struct VtebPeerTable {
+    float* board[8];
+    int* flags[8];
+};
+
+// grid (world, 1, 1), block 256: CTA p copies this rank's state into peer p's board.
+extern "C" __global__ void __launch_bounds__(256) vteb_push_shard_state_kernel(
+    const float* __restrict__ state, VtebPeerTable peers, int world, int rank, int layer, int n_layers,
+    int state_floats, const int* __restrict__ step_word)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int p = blockIdx.x;
+    if (p >= world) return;
+    const int step = *step_word;
+    const long long slot = ((long long)(step & 1) * n_layers + layer) * world + rank;
+    float* dst = peers.board[p] + slot * state_floats;
+    for (int i = threadIdx.x; i < state_floats; i += blockDim.x) dst[i] = state[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        volatile int* flag = peers.flags[p] + slot;
+        *flag = step + 1;
+        __threadfence_system();
+    }
+}
+
+// grid (rows, 1, 1), block (D, 1, 1): waits for every rank's flag, then merges.
+extern "C" __global__ void vteb_merge_shard_states_p2p_kernel(
+    const float* __restrict__ board, const int* __restrict__ flags, float* __restrict__ out, int world, int rows,
+    int head_dim, int layer, int n_layers, const int* __restrict__ step_word, int* __restrict__ status)
+{
+    __shared__ int ok_sh;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int step = *step_word;
+    const long long slot0 = ((long long)(step & 1) * n_layers + layer) * world;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int r = 0; r < world && ok; ++r) {
+            const volatile int* flag = flags + slot0 + r;
+            while (*flag != step + 1) {
+                if (clock64() - t0 > 4000000000ll) { ok = 0; break; }   // ~2 s: give up, report, return
+            }
+        }
+        __threadfence_system();
+        if (!ok) atomicCAS(status, 0, kStatusGridTimeout);
+        ok_sh = ok;
+    }
+    __syncthreads();
+    if (!ok_sh) return;
+    const int row = blockIdx.x, pitch = head_dim + 2;
+    const long long state_floats = (long long)rows * pitch;
+    const float* base = board + slot0 * state_floats;
+    float M = kNeutralM;
+    for (int r = 0; r < world; ++r) M = fmaxf(M, __ldcg(base + r * state_floats + (long long)row * pitch + head_dim));
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.f, L = 0.f;
+        for (int r = 0; r < world; ++r) {
+            const float* st = base + r * state_floats + (long long)row * pitch;
+            const float m = __ldcg(st + head_dim);
+            const float w = (m <= -1e29f) ? 0.f : __expf(m - M);
+            if (w != 0.f) { acc = fmaf(__ldcg(st + d), w, acc); L = fmaf(__ldcg(st + head_dim + 1), w, L); }
+        }
+        out[(long long)row * head_dim + d] = acc / fmaxf(L, 1e-20f);
+    }
+}
+
+// One thread: the decode step is over, the next one uses the other board parity.
+extern "C" __global__ void vteb_advance_step_kernel(int* __restrict__ step_word)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0) *step_word = *step_word + 1;
+}
+
 #include "split_kv_fast.cuh"

@@ -499,6 +499,32 @@ int vteb_nccl_comm_destroy(void* comm) {
     return check_nccl(g_nccl.CommDestroy(comm), "ncclCommDestroy");
 }
 
+// ---- peer memory ---------------------------------------------------------------
+int vteb_ipc_get_handle(void* dev_ptr, void* handle64) {
+    REQUIRE_INIT();
+    if (!dev_ptr || !handle64) return fail(VTEB_ERR_INVALID_ARGUMENT, "null ipc argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "ipc handle size");
+    cudaIpcMemHandle_t h;
+    int rc = check_rt(cudaIpcGetMemHandle(&h, dev_ptr), "cudaIpcGetMemHandle");
+    if (rc) return rc;
+    memcpy(handle64, &h, sizeof(h));
+    return 0;
+}
+
+int vteb_ipc_open_handle(const void* handle64, void** dev_ptr) {
+    REQUIRE_INIT();
+    if (!dev_ptr || !handle64) return fail(VTEB_ERR_INVALID_ARGUMENT, "null ipc argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return check_rt(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+}
+
+int vteb_ipc_close_handle(void* dev_ptr) {
+    REQUIRE_INIT();
+    if (!dev_ptr) return fail(VTEB_ERR_INVALID_ARGUMENT, "null ipc pointer");
+    return check_rt(cudaIpcCloseMemHandle(dev_ptr), "cudaIpcCloseMemHandle");
+}
+
 // ---- split-KV decode attention ---------------------------------------------
 static int fill_plan(int num_q_heads, int num_kv_heads, int head_dim, int lite, vteb_fast_plan* plan) {
     if (!plan) return fail(VTEB_ERR_INVALID_ARGUMENT, "null plan");
