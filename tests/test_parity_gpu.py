@@ -417,3 +417,32 @@ def test_lite_cta_shape_matches(cuda_runtime, codegen, name):
     q, k, v, off = make_layer_inputs(cfg, 0)
     out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, variant="lite")
     assert_parity(out, np.load(GOLD / "attn_c2_layer0.npz")["out"], tight=2e-5)
+
+
+def test_unsplit_path_stores_the_output_in_one_launch(cuda_runtime, codegen):
+    """One split: the split launch normalises and stores the output itself (no combine
+    launch); chosen automatically for short configured contexts."""
+    for name in ("ragged_d64", "group8_d128", "outlier_d256", "mha_d128"):
+        cfg, lens = SMALL_CASES[name]
+        q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
+        ref = orc.decode_attention(q, k, v, off)
+        for f32 in (True, False):
+            ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 1, num_splits=1,
+                                         output_f32=f32)
+            try:
+                assert len(ex.dispatcher.build_launches(0, ex.tensor_mapping, ex.offsets.ptr, batch=cfg.batch)) == 2
+                ex.upload_layer(0, q, k, v)
+                for _ in range(2):
+                    out = ex.execute_decode_batch(off)[0]
+                    if f32:
+                        assert_parity(out, ref)
+                    else:
+                        assert np.max(np.abs(out.astype(np.float32) - ref)) <= 4e-3
+            finally:
+                ex.cleanup()
+    short = DecodeConfig("short", 23, 2, 12, 2, 128, 100, 100, 1)
+    ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(short), 2, 100, 1)
+    try:
+        assert ex.dispatcher.max_chunks == 1
+    finally:
+        ex.cleanup()

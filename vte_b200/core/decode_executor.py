@@ -164,8 +164,8 @@ class DecodeAttentionExecutor:
         self.hip.programmatic_launch = self.programmatic
         try:
             if not self.use_graph:
-                per_layer = (1 if self.dispatcher.fused_combine else 2) + (1 if self.with_append else 0)
-                self.kernel_launches_per_step = per_layer * self.L
+                n = len(self.dispatcher.build_launches(0, self.tensor_mapping, self.offsets.ptr, batch=self.B))
+                self.kernel_launches_per_step = (n if self.with_append else n - 1) * self.L
                 return
             self.hip.stream_begin_capture()
             try:

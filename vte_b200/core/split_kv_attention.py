@@ -31,6 +31,8 @@ SPLIT_KV_CHUNK_SIZE = 32          # the reference's historical chunk (RX 7600, 3
 MAX_SPLITS = 256
 TARGET_CHUNK_POSITIONS = 256      # smallest chunk length aimed at when many sequences share the GPU
 FLAG_WRITE_EMPTY_O = 1
+FLAG_DIRECT_OUTPUT = 2
+UNSPLIT_MAX_CONTEXT = 128         # below this, one CTA per (sequence, head group) finishes before a combine could launch
 
 
 def _chunk_size_for_cus(num_cus: int) -> int:
@@ -64,6 +66,8 @@ def choose_split_count(num_sms: int, batch: int, n_hgroups: int, context_length:
     that ragged lengths balance through the work queue while the fp32 partials
     stay a few percent of the K/V bytes.
     """
+    if context_length <= UNSPLIT_MAX_CONTEXT:
+        return 1                                   # unsplit: the split launch stores the output itself
     if batch * n_hgroups <= 1:
         return max(1, min(MAX_SPLITS, num_sms))
     if batch == 1:
@@ -302,12 +306,19 @@ class SplitKVAttentionDispatcher:
             if not (next_k and next_v) or next_k % 16 or next_v % 16:
                 next_k = next_v = 0
         out_kind = 3 if self.emit_state else (2 if self.output_f32 else 1)
+        # One split and an ordinary output: the split launch normalises and stores the attention
+        # output itself (the reference's unsplit kernel, flash_attention.hip.template:29-113, in one
+        # launch).  Needs one CTA per work item, because nothing resets the work queue afterwards.
+        direct = C == 1 and not self.emit_state and not self.strict_empty_splits and items <= self.num_sms * (3 if self.lite else 1)
+        if direct:
+            flags |= FLAG_DIRECT_OUTPUT
+        pass_output = self.fused_combine or direct
         partial_args = reference_partial_args + [
             ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4),
             vp(next_k), vp(next_v),
-            vp(output_ptr if self.fused_combine else 0), ci(out_kind if self.fused_combine else 0)]
+            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0)]
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
-        if self.fused_combine:
+        if self.fused_combine or direct:
             return [append, partial]
         if self._rows_combine:
             rows = batch * Hq

@@ -40,6 +40,22 @@ struct FastArgs {
 };
 
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
+constexpr int kFlagDirectOutput = 2;  // max_chunks == 1: normalise and store the attention output here, no partials
+
+// Stores four (or two) normalised output values; out_kind 1 = fp16, 2 = fp32.
+__device__ __forceinline__ void store_out4(void* output, int out_kind, long long idx, float4 v) {
+    if (out_kind == 2) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(output) + idx) = v;
+    } else {
+        __half2* o = reinterpret_cast<__half2*>(reinterpret_cast<__half*>(output) + idx);
+        o[0] = __floats2half2_rn(v.x, v.y);
+        o[1] = __floats2half2_rn(v.z, v.w);
+    }
+}
+__device__ __forceinline__ void store_out2(void* output, int out_kind, long long idx, float2 v) {
+    if (out_kind == 2) *reinterpret_cast<float2*>(reinterpret_cast<float*>(output) + idx) = v;
+    else *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(output) + idx) = __floats2half2_rn(v.x, v.y);
+}
 
 // Shared-memory control block (first kCtrlBytes of dynamic shared memory).
 constexpr int kBarFull = 0;                        // 8 barriers
@@ -280,6 +296,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             // Later items come from the shared ticket, which the previous combine
             // launch reset: it may only be touched once that launch has completed.
             if (!dep_done) { grid_dependency_wait(); dep_done = true; }
+            if (a.flags & kFlagDirectOutput) { item = total_items; continue; }   // unsplit: one item per CTA, go publish the stop tile
             int next = 0;
             if (lane == 0) next = gridDim.x + atomicAdd(a.ticket, 1);
             item = __shfl_sync(0xffffffffu, next, 0);
@@ -518,7 +535,15 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 l_own += __shfl_xor_sync(0xffffffffu, l_own, 1);
                 l_own += __shfl_xor_sync(0xffffffffu, l_own, 2);
                 const bool empty1 = (flags & kTileEmpty) != 0;
-                if (g < group) {
+                if (g < group && (a.flags & kFlagDirectOutput)) {
+                    // unsplit: this warp holds the whole sequence's state for its rows
+                    const long long row = (long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
+                                          (long long)hh * group + g;
+                    const float inv = 1.f / fmaxf(l_own, 1e-20f);
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+                        store_out2(a.output, a.out_kind, row * D + n * 8 + 2 * t, make_float2(o_acc[n][0] * inv, o_acc[n][1] * inv));
+                } else if (g < group) {
                     const long long stat = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
                                             (long long)hh * group + g) * a.max_chunks + item_c;
                     if (!empty1 || (a.flags & kFlagWriteEmptyO)) {
@@ -602,6 +627,17 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         acc[i].z = fmaf(ow[w][i].z, wt, acc[i].z); acc[i].w = fmaf(ow[w][i].w, wt, acc[i].w);
                     }
                 }
+                if (a.flags & kFlagDirectOutput) {
+                    const long long row = (long long)item_b * a.num_q_heads + (long long)item_hgroup * heads_item + hq;
+                    const float inv = 1.f / fmaxf(ll, 1e-20f);
+                    if (col_ok) {
+#pragma unroll
+                        for (int i = 0; i < NV; ++i)
+                            store_out4(a.output, a.out_kind, row * D + i * 128 + lane * 4,
+                                       make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv));
+                    }
+                    continue;
+                }
                 const long long stat = stat0 + (long long)hq * a.max_chunks;
                 if (write_o && col_ok) {
 #pragma unroll
@@ -621,7 +657,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
     }
 
-    if (kLite || a.out_kind == 0) return;
+    if (kLite || a.out_kind == 0 || (a.flags & kFlagDirectOutput)) return;
     // ===================================================================== in-launch combine
     // (needs all eight consumer warps; the host only asks for it then)
     // 1. every consumer warp's partial stores are fenced, then counted on a CTA barrier
