@@ -362,13 +362,17 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     if (warp >= plan.active_warps) return;
 
     // ===================================================================== consumers
-    const int hh = warp % plan.hg;        // KV head within the group
-    const int sub = warp / plan.hg;       // which of the wph interleaved block streams
+    // warp = (sub * DS + dhalf) * hg + hh
+    constexpr int DS = (D == 256) ? 2 : 1;              // warps sharing one (head, block), split by output columns
+    const int hh = warp % plan.hg;                      // KV head within the group
+    const int dhalf = (warp / plan.hg) % DS;            // which part of the output columns this warp owns
+    const int sub = warp / (plan.hg * DS);              // which of the wph interleaved block streams
     const int wph_mask = plan.wph - 1;    // wph is a power of two
     const int g = lane >> 2, t = lane & 3;
     const float scale2 = a.scale * kLog2e;
     constexpr int KS = D / 16;            // k-steps of the QK^T product
-    constexpr int NT = D / 8;             // 8-wide output column tiles
+    constexpr int NT = D / 8 / DS;        // 8-wide output column tiles owned by this warp
+    constexpr int DW = D / DS;            // output columns owned by this warp
     const int blocks_per_tile = plan.tile / kBlockPos;
 
     // Q operand fragments of this warp's KV head: word i of lane L at q_frag[i * 32].
@@ -399,7 +403,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // Lane-constant parts of the ldmatrix addresses.
     const int k_lane_off = ((lane & 7) + ((lane >> 4) << 3)) * plan.row_pitch + (((lane >> 3) & 1) * 8 + hh * D) * 2;
-    const int v_lane_off = ((lane & 7) + (((lane >> 3) & 1) << 3)) * plan.row_pitch + ((lane >> 4) * 8 + hh * D) * 2;
+    const int v_lane_off = ((lane & 7) + (((lane >> 3) & 1) << 3)) * plan.row_pitch + ((lane >> 4) * 8 + hh * D + dhalf * DW) * 2;
     const int v_tile_off = plan.tile * plan.row_pitch;
 
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
@@ -542,17 +546,18 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     const float inv = 1.f / fmaxf(l_own, 1e-20f);
 #pragma unroll
                     for (int n = 0; n < NT; ++n)
-                        store_out2(a.output, a.out_kind, row * D + n * 8 + 2 * t, make_float2(o_acc[n][0] * inv, o_acc[n][1] * inv));
+                        store_out2(a.output, a.out_kind, row * D + dhalf * DW + n * 8 + 2 * t,
+                                   make_float2(o_acc[n][0] * inv, o_acc[n][1] * inv));
                 } else if (g < group) {
                     const long long stat = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
                                             (long long)hh * group + g) * a.max_chunks + item_c;
                     if (!empty1 || (a.flags & kFlagWriteEmptyO)) {
-                        float* out = a.partial_o + stat * D + 2 * t;
+                        float* out = a.partial_o + stat * D + dhalf * DW + 2 * t;
 #pragma unroll
                         for (int n = 0; n < NT; ++n)
                             *reinterpret_cast<float2*>(out + n * 8) = make_float2(o_acc[n][0], o_acc[n][1]);
                     }
-                    if (t == 0) {
+                    if (t == 0 && dhalf == 0) {
                         a.partial_m[stat] = empty1 ? kNeutralM : m_run * kLn2;
                         a.partial_l[stat] = empty1 ? 0.f : l_own;
                     }
@@ -574,7 +579,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 float* dst = merge + ((size_t)warp * group + g) * pitch;
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
-                    *reinterpret_cast<float2*>(dst + n * 8 + 2 * t) = make_float2(o_acc[n][0], o_acc[n][1]);
+                    *reinterpret_cast<float2*>(dst + dhalf * DW + n * 8 + 2 * t) = make_float2(o_acc[n][0], o_acc[n][1]);
                 if (t == 0) { dst[D + 4] = m_run; dst[D + 5] = l_quad; }
             }
             __syncwarp();
@@ -593,8 +598,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             const bool write_o = !empty || (a.flags & kFlagWriteEmptyO);
             for (int hq = warp; hq < heads_item; hq += plan.active_warps) {
                 const int kvh = hq / group, row = hq - kvh * group;
-                const float* src0 = merge + ((size_t)kvh * group + row) * pitch;        // warp (0 * hg + kvh)
-                const size_t wstride = (size_t)plan.hg * group * pitch;                  // next warp of the same head
+                const float* src0 = merge + ((size_t)kvh * group + row) * pitch;        // warp (sub 0, half 0, kvh)
+                const size_t hstride = (size_t)plan.hg * group * pitch;                  // same sub, next column half
+                const size_t wstride = hstride * DS;                                     // next sub of the same head
                 constexpr int NV = (D + 127) / 128;                                      // float4 columns per lane
                 const bool col_ok = (D >= 128) || lane < D / 4;
                 float mw[CW], lw[CW];
@@ -606,8 +612,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     mw[w] = on ? src[D + 4] : kNeutralM;
                     lw[w] = on ? src[D + 5] : 0.f;
 #pragma unroll
-                    for (int i = 0; i < NV; ++i)
-                        ow[w][i] = (on && col_ok) ? *reinterpret_cast<const float4*>(src + i * 128 + lane * 4)
+                    for (int i = 0; i < NV; ++i)   // float4 group i lies in column half (i * 128) / DW, written by that half's warp
+                        ow[w][i] = (on && col_ok) ? *reinterpret_cast<const float4*>(src + ((i * 128) / DW) * hstride + i * 128 + lane * 4)
                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
                 float mm = kNeutralM;

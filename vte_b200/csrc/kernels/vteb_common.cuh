@@ -101,10 +101,14 @@ __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_h
     if (cap > cw) cap = cw;
     int hg = 1;
     for (int d = 1; d <= cap; ++d) if (num_kv_heads % d == 0) hg = d;
+    // 256-wide heads: two warps share a (head, block), each owning half of the output
+    // columns (both compute the scores); halves the accumulator registers per warp.
+    const int dsplit = (head_dim == 256) ? 2 : 1;
     p.hg = hg;
     p.n_hgroups = num_kv_heads / hg;
-    p.wph = cw / hg;
-    p.active_warps = p.wph * hg;
+    p.wph = cw / (hg * dsplit);
+    if (p.wph < 1) return p;
+    p.active_warps = p.wph * hg * dsplit;
     p.row_bytes = hg * head_dim * 2;
     p.row_pitch = p.row_bytes + 16;
     int tile = ((lite ? 8192 : 16384) / p.row_bytes) / kBlockPos * kBlockPos;
