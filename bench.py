@@ -230,7 +230,8 @@ def run_ours(args, rank, world, local_rank):
                                  min_chunk=None if args.min_chunk < 0 else args.min_chunk,
                                  programmatic=not args.no_pdl, compat=args.compat,
                                  prefetch_next_layer=not args.no_prefetch,
-                                 fused_combine=args.fuse, variant=args.variant)
+                                 fused_combine=args.fuse, variant=args.variant, rope=args.rope,
+                                 rope_theta=cfg.rope_theta or 1e6)
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
@@ -260,7 +261,10 @@ def run_ours(args, rank, world, local_rank):
     # ---- parity of what is being timed (layer 0 against the oracle)
     parity = None
     out = ex.execute_decode_batch(offsets)
-    if 0 in host_layers:
+    if args.rope != "off":
+        # the step rewrites the last cache row and rotates its inputs: checked by the GPU tests instead
+        parity = {"skipped": "rotation modes are checked against the oracle by the GPU tests"}
+    elif 0 in host_layers:
         from oracle import attention_oracle as orc
         q, k, v, off = host_layers[0]
         max_abs, rel = orc.parity_metrics(out[0], orc.decode_attention(q, k, v, off))
@@ -317,7 +321,10 @@ def run_ours(args, rank, world, local_rank):
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
                                    "programmatic_dependent_launch": not args.no_pdl,
                                    "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1,
-                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, lite CTAs" if ex.dispatcher.lite else "fast, full CTAs")}),
+                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, lite CTAs" if ex.dispatcher.lite else "fast, full CTAs"),
+                                   "step_contents": {"off": "split + combine per layer",
+                                                     "separate": "rotation launch + cache append + split + combine per layer",
+                                                     "fused": "cache append with K rotation + split with Q rotation + combine per layer"}[args.rope]}),
             "us_per_layer_token": step_s * 1e6 / n_layers / global_cfg.batch,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
             "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
@@ -439,7 +446,7 @@ def kernel_durations(rt, ex, n_layers, reps=10):
     includes the in-graph launch gap between consecutive kernels."""
     disp = ex.dispatcher
     name = ("flash_attention_split_kv_partial_kernel" if disp.compat else
-            f"vteb_split_kv_partial_{'lite_' if disp.lite else ''}d{disp.head_dim}_kernel")
+            f"vteb_split_kv_partial_{'lite_' if disp.lite else 'rope_' if disp.fuse_rope else ''}d{disp.head_dim}_kernel")
     out = {}
     kinds = ((0, "split_us"),) if disp.fused_combine else ((0, "split_us"), (1, "combine_us"))
     out["combine_us"] = 0.0
@@ -500,6 +507,9 @@ def main():
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")
+    ap.add_argument("--rope", default="off", choices=["off", "separate", "fused"],
+                    help="also run the rotary embedding and the cache append inside the step: as the standalone "
+                         "rotation launch, or folded into the append (K) and the split kernel's Q load")
     ap.add_argument("--device-fill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -25,6 +25,12 @@ What each function restates (paths are relative to the reference project):
 * `kv_cache_append`              vte/compiler/templates/rdna/kv_cache_append.hip.template:23-38
 * `rope_tables`, `rope_neox`     vte/compiler/rope_cache_builder.py:42-97 and
                                  vte/compiler/templates/rdna/rope.hip.template:82-97
+* `rope_apply`                   vte/compiler/templates/rdna/rope.hip.template:55-97
+                                 (the three rotation types; type 0 and type 2
+                                 are pinned through the reference's own numpy
+                                 rotation, type 1 has no Python counterpart in
+                                 the reference and is a restatement of the
+                                 template alone: parity unpinned for type 1)
 * `chunk_size_for_cus`           vte/core/split_kv_attention.py:40-49
 """
 from __future__ import annotations
@@ -216,6 +222,51 @@ def rope_neox(x, cos_row, sin_row):
     s = sin_row[:half].astype(np.float32)
     lo, hi = xf[..., :half], xf[..., half:]
     return np.concatenate([lo * c - hi * s, lo * s + hi * c], axis=-1).astype(np.float16)
+
+
+def rope_apply(x, cos_row, sin_row, rope_type=0, rotary_dim=None):
+    """Rotation of [..., D] fp16 vectors at one position for the reference's
+    three `rope_type`s (rope.hip.template:55-97), fp32 arithmetic with each
+    product rounded separately, fp16 on store.
+
+    0  split-half over the whole head: row length D, pair (j, j + D/2).
+    1  interleaved: pair (2i, 2i+1) uses entry i of a row of length D
+       (template lines 57-66).
+    2  split-half inside the first `rotary_dim` channels only: row length
+       `rotary_dim`, pair (j, j + rotary_dim/2); the remaining channels pass
+       through untouched (template lines 67-81)."""
+    D = x.shape[-1]
+    xf = x.astype(np.float32)
+    cos_row = np.asarray(cos_row).astype(np.float32)
+    sin_row = np.asarray(sin_row).astype(np.float32)
+    if rope_type == 1:
+        c, s = cos_row[:D // 2], sin_row[:D // 2]
+        x0, x1 = xf[..., 0::2], xf[..., 1::2]
+        out = np.empty_like(xf)
+        out[..., 0::2] = x0 * c - x1 * s
+        out[..., 1::2] = x0 * s + x1 * c
+        return out.astype(np.float16)
+    rot = D if rope_type == 0 else int(rotary_dim)
+    half = rot // 2
+    c, s = cos_row[:half], sin_row[:half]
+    lo, hi = xf[..., :half], xf[..., half:rot]
+    out = xf.copy()
+    out[..., :half] = lo * c - hi * s
+    out[..., half:rot] = lo * s + hi * c
+    return out.astype(np.float16)
+
+
+def rope_step(q, k, cos_table, sin_table, kv_offsets, rope_type=0, rotary_dim=None):
+    """What `rope_kernel` does in one decode step (seq_len 1): rotates
+    q [B, Hq, D] and k [B, Hkv, D] of sequence b at position kv_offsets[b]
+    (rope.hip.template:41-55).  Tables are [max_seq, D] (types 0, 1) or
+    [max_seq, rotary_dim] (type 2).  Returns new arrays."""
+    q2, k2 = q.copy(), k.copy()
+    for b in range(q.shape[0]):
+        pos = int(kv_offsets[b])
+        q2[b] = rope_apply(q[b], cos_table[pos], sin_table[pos], rope_type, rotary_dim)
+        k2[b] = rope_apply(k[b], cos_table[pos], sin_table[pos], rope_type, rotary_dim)
+    return q2, k2
 
 
 def merge_shard_states(states):

@@ -53,6 +53,27 @@ def reference_decode(ref_fn, cfg, q, k, v, offsets):
     return out
 
 
+def make_rope_partial(vr, RoPECacheBuilder):
+    """Partial split-half rotation (rope_type 2): the reference builds the table with
+    head_dim = rotary_dim (vte/compiler/qwen3_5_mapper.py:292-298) and rotates only
+    those channels, so its own numpy rotation applied to the first `rotary_dim`
+    channels is the pin."""
+    D, rot, theta, max_seq = 256, 64, 1e7, 4096
+    cos, sin = RoPECacheBuilder(max_seq_len=max_seq, head_dim=rot, rope_theta=theta).build_cache()
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((8, D), dtype=np.float32).astype(np.float16)
+    positions = np.array([0, 1, 77, 4095])
+    rotated = np.zeros((len(positions),) + x.shape, dtype=np.float16)
+    for pi, pos in enumerate(positions):
+        xin = np.zeros((1, pos + 1, x.shape[0], rot), dtype=np.float32)
+        xin[0, pos] = x[:, :rot].astype(np.float32)
+        y = vr.apply_rope_reference(xin, cos.astype(np.float32), sin.astype(np.float32), pos + 1, x.shape[0], rot)
+        rotated[pi] = x
+        rotated[pi, :, :rot] = y[0, pos].astype(np.float16)
+    np.savez_compressed(HERE / "rope_partial.npz", x=x, positions=positions, cos_rows=cos[positions],
+                        sin_rows=sin[positions], x_rotated=rotated, rotary_dim=np.array(rot), theta=np.array(theta))
+
+
 def main(ref_root: str):
     sys.path.insert(0, ref_root)
     sys.path.insert(0, str(Path(ref_root) / "tools"))
@@ -90,11 +111,24 @@ def main(ref_root: str):
     np.savez_compressed(HERE / "rope.npz", rows=rows, cos_rows=cos[rows], sin_rows=sin[rows], x=x,
                         x_rotated=np.stack(rotated), position=np.array(pos), theta=np.array(theta))
 
+    make_rope_partial(vr, RoPECacheBuilder)
+
     # --- chunk-size rule
     cus = np.array([0, -1, 1, 8, 16, 20, 32, 48, 64, 96, 128, 148, 296, 1024])
     np.savez_compressed(HERE / "chunk_rule.npz", cus=cus, chunk=np.array([_chunk_size_for_cus(int(c)) for c in cus]))
     print("done")
 
 
+def main_rope_partial_only(ref_root: str):
+    sys.path.insert(0, ref_root)
+    sys.path.insert(0, str(Path(ref_root) / "tools"))
+    import validate_rope as vr               # reference module
+    from vte.compiler.rope_cache_builder import RoPECacheBuilder
+    make_rope_partial(vr, RoPECacheBuilder)
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # `--only-rope-partial` writes that one fixture and leaves the others' bytes alone
+    argv = [a for a in sys.argv[1:] if not a.startswith("--")]
+    root = argv[0] if argv else "/root/reference"
+    (main_rope_partial_only if "--only-rope-partial" in sys.argv else main)(root)

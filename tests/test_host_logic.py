@@ -172,6 +172,50 @@ def test_fused_launch_list_is_append_plus_one_launch():
     assert not d2.fused_combine and len(d2.build_launches(0, mapping(), 0x7200_0000_0000)) == 3
 
 
+def test_fused_rope_launch_list_and_standalone_rotation_launch():
+    meta = {'attention.head_count': 8, 'attention.head_count_kv': 2, 'attention.key_length': 256,
+            'rope_type': 2, 'rotary_dim': 64}
+    d, rt, cg, _ = make_dispatcher(meta, context_length=4096, batch_size=4, fuse_rope=True)
+    m = mapping()
+    with pytest.raises(CudaSafetyError):
+        d.build_launches(0, m, 0x7200_0000_0000, batch=4)              # no tables in the mapping
+    m['rope_cos'], m['rope_sin'] = 0x7300_0000_0000, 0x7300_1000_0000
+    launches = d.build_launches(0, m, 0x7200_0000_0000, batch=4)
+    symbols = [s for _, s in rt.loaded]
+    assert symbols[:2] == ["kv_cache_append_rope_kernel", "vteb_split_kv_partial_rope_d256_kernel"]
+    (fa, aa, ga, ba, sa), (fp, ap, gp, bp, sp) = launches[:2]
+    assert len(aa) == len(KERNEL_SIGNATURES["kv_cache_append_rope_kernel"]) == 12
+    assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_rope_d256_kernel"]) == 27
+    for args in (aa, ap):
+        assert [a.value for a in args[-4:]] == [0x7300_0000_0000, 0x7300_1000_0000, 2, 64]
+    assert ga == (4, 2, 1) and ba == (256, 1, 1)
+    # the standalone launch: the reference's eleven arguments and its grid rule
+    fn, args, grid, block, smem = d.build_rope_launch(m, 0x7200_0000_0000, batch=4)
+    assert rt.loaded[-1][1] == "rope_kernel" and len(args) == len(KERNEL_SIGNATURES["rope_kernel"]) == 11
+    assert grid == (8 * 256 // 256, 4, 1) and block == (256, 1, 1) and smem == 0
+    assert [a.value for a in args[4:8]] == [1, 8, 2, 256] and [a.value for a in args[9:]] == [2, 64]
+    # options the rotation cannot be combined with, and widths the kernel has no code for
+    for kw in ({'compat': True}, {'variant': 'lite'}):
+        meta128 = {'attention.head_count': 12, 'attention.head_count_kv': 2, 'attention.key_length': 128}
+        with pytest.raises(CudaSafetyError):
+            make_dispatcher(meta128, fuse_rope=True, **kw)
+    with pytest.raises(CudaSafetyError):
+        make_dispatcher(dict(meta, rotary_dim=48), fuse_rope=True)
+    with pytest.raises(CudaSafetyError):
+        make_dispatcher(dict(meta, rope_type=3), fuse_rope=True)
+
+
+def test_rope_cache_builder_matches_the_pinned_tables():
+    from oracle import attention_oracle as orc
+    from vte_b200.workloads import build_rope_cache
+    for width, theta in ((128, 1e6), (64, 1e7), (256, 1e4)):
+        cos, sin = build_rope_cache(300, width, theta)
+        oc, os_ = orc.rope_tables(300, width, theta)
+        assert cos.dtype == np.float16 and cos.shape == (300, width)
+        assert np.array_equal(cos, oc) and np.array_equal(sin, os_)
+        assert np.array_equal(cos[:, :width // 2], cos[:, width // 2:])
+
+
 def test_lite_shape_is_opt_in():
     d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, variant="lite")
     assert d.lite and d.max_chunks == 148

@@ -92,6 +92,40 @@ def test_rope_matches_reference_tables_and_rotation():
     assert np.array_equal(rope_rotate_neox(gold["x"], pos, theta), gold["x_rotated"])
 
 
+def test_rope_types_match_reference_rotation():
+    # type 0 through the general entry point equals the pinned split-half rotation
+    gold = np.load(GOLD / "rope.npz")
+    c, s = orc.rope_row(int(gold["position"]), 128, float(gold["theta"]))
+    assert np.array_equal(orc.rope_apply(gold["x"], c, s, 0), gold["x_rotated"])
+    # type 2 (partial split-half): the reference's numpy rotation of the first rotary_dim channels
+    part = np.load(GOLD / "rope_partial.npz")
+    rot, theta = int(part["rotary_dim"]), float(part["theta"])
+    for pi, pos in enumerate(part["positions"]):
+        c, s = orc.rope_row(int(pos), rot, theta)
+        assert np.array_equal(c, part["cos_rows"][pi]) and np.array_equal(s, part["sin_rows"][pi])
+        y = orc.rope_apply(part["x"], c, s, 2, rot)
+        assert np.array_equal(y, part["x_rotated"][pi])
+        assert np.array_equal(y[:, rot:], part["x"][:, rot:])          # untouched channels
+    # type 2 with rotary_dim == D is type 0
+    c, s = orc.rope_row(5, 128, 1e4)
+    assert np.array_equal(orc.rope_apply(gold["x"], c, s, 2, 128), orc.rope_apply(gold["x"], c, s, 0))
+    # type 1 (interleaved; no Python counterpart in the reference): a rotation of adjacent pairs,
+    # so pair norms survive up to fp16 rounding and position 0 is the identity
+    x = gold["x"]
+    y = orc.rope_apply(x, c, s, 1)
+    n_in = np.hypot(x[:, 0::2].astype(np.float64), x[:, 1::2].astype(np.float64))
+    n_out = np.hypot(y[:, 0::2].astype(np.float64), y[:, 1::2].astype(np.float64))
+    assert np.max(np.abs(n_in - n_out)) < 4e-3
+    c0, s0 = orc.rope_row(0, 128, 1e4)
+    assert np.array_equal(orc.rope_apply(x, c0, s0, 1), x)
+    # rope_step rotates every sequence at its own position
+    cos_t, sin_t = orc.rope_tables(16, 128, 1e4)
+    q = np.stack([x, x]); k = q[:, :2]
+    q2, k2 = orc.rope_step(q, k, cos_t, sin_t, np.array([3, 9]), 0)
+    assert np.array_equal(q2[1], orc.rope_apply(x, cos_t[9], sin_t[9], 0))
+    assert np.array_equal(k2[0], orc.rope_apply(x[:2], cos_t[3], sin_t[3], 0))
+
+
 def test_chunk_rule_matches_reference():
     gold = np.load(GOLD / "chunk_rule.npz")
     from vte_b200.core.split_kv_attention import _chunk_size_for_cus

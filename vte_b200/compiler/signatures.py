@@ -7,7 +7,8 @@ reference paid for a missing check of this kind with a GPU hang
 kernels list exactly the arguments of
 kv_cache_append.hip.template:13-22,
 flash_attention_split_kv_partial.hip.template:31-45 and
-flash_attention_split_kv_reduce.hip.template:14-22.
+flash_attention_split_kv_reduce.hip.template:14-22; `rope_kernel` lists those of
+rope.hip.template:17-37 (vte/core/kernel_arg_builder.py:44-56).
 """
 import ctypes
 
@@ -16,17 +17,23 @@ P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _REFERENCE_PARTIAL = [P, P, P, P, P, P, I, I, I, F, P, I, I]
 _FAST_PARTIAL = _REFERENCE_PARTIAL + [I, I, I, P, P, P, P, P, P, I]
 # ... batch, min_chunk, flags, seq_order, ticket, status, next K, next V, output, out_kind
+_ROPE_TAIL = [P, P, I, I]                                 # cos table, sin table, rope_type, rotary_dim
 _REDUCE = [P, P, P, P, I, I, I]
 _FAST_COMBINE = _REDUCE + [I, P]                          # dsplit, ticket
 
 KERNEL_SIGNATURES = {
     "kv_cache_append_kernel": [P, P, P, P, I, I, P, I],
+    "kv_cache_append_rope_kernel": [P, P, P, P, I, I, P, I] + _ROPE_TAIL,
+    "rope_kernel": [P, P, P, P, I, I, I, I, P, I, I],
     "flash_attention_split_kv_partial_kernel": _REFERENCE_PARTIAL,
     "flash_attention_split_kv_reduce_kernel": _REDUCE,
     "flash_attention_split_kv_reduce_f32_kernel": _REDUCE,
     "vteb_split_kv_partial_d64_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_d128_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_d256_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL,
+    "vteb_split_kv_partial_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL,
+    "vteb_split_kv_partial_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL,
     "vteb_split_kv_partial_lite_d64_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_lite_d128_kernel": _FAST_PARTIAL,
     "vteb_split_kv_combine_f16_kernel": _FAST_COMBINE,
@@ -42,6 +49,7 @@ KERNEL_SIGNATURES = {
 # template name (what the reference passes to load_kernel_safe) -> source file
 TEMPLATE_SOURCES = {
     "kv_cache_append": "decode_attention.cu",
+    "rope": "decode_attention.cu",
     "flash_attention_split_kv_partial": "decode_attention.cu",
     "flash_attention_split_kv_reduce": "decode_attention.cu",
     "decode_attention": "decode_attention.cu",

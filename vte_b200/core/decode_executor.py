@@ -32,8 +32,17 @@ class DecodeAttentionExecutor:
                  with_append: bool = False, fixed_chunk_size=None, min_chunk: Optional[int] = None,
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
                  emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
-                 fused_combine: Optional[bool] = None, variant: str = "full"):
+                 fused_combine: Optional[bool] = None, variant: str = "full", rope: str = "off",
+                 rope_theta: float = 1e6):
         self.hip = hip
+        # rope: "off" = Q and K arrive rotated; "separate" = the reference's standalone rotation
+        # launch runs before the append (rotating the projections in place); "fused" = the append
+        # rotates K and the split kernel rotates Q.  Either way the step includes the append.
+        if rope not in ("off", "separate", "fused"):
+            raise CudaSafetyError(f"rope must be off, separate or fused, not {rope!r}")
+        self.rope = rope
+        if rope != "off":
+            with_append = True
         self.metadata = dict(metadata)
         self.B = int(batch_size)
         self.S = int(context_length)
@@ -65,7 +74,7 @@ class DecodeAttentionExecutor:
         self._owns_allocator = allocator is None
         if allocator is None:
             need = (2 * self.n_kv * (self.kv_bytes + 256) + self.L * (self.q_bytes + 2 * self.kvnew_bytes
-                    + self.out_bytes + 1024) + (64 << 20))
+                    + self.out_bytes + 1024) + (64 << 20) + (4 * self.S * self.D + 4096 if rope != "off" else 0))
             free_b, total_b = hip.get_real_mem_info()
             allocator = SlabAllocator(hip, total_b, requested_pool_size=need)
             allocator.initialize()
@@ -74,7 +83,8 @@ class DecodeAttentionExecutor:
             hip, codegen, self.metadata, allocator=allocator, context_length=self.S, batch_size=self.B,
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
-            prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant)
+            prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant,
+            fuse_rope=(rope == "fused"))
 
         A = allocator.allocate
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
@@ -94,6 +104,18 @@ class DecodeAttentionExecutor:
             self.tensor_mapping[f'blk.{l}.attention.output'] = self.out_all.ptr + l * self.out_bytes
             self.tensor_mapping[f'blk.{l}.kv_cache.k'] = self.k_cache[l % self.n_kv]
             self.tensor_mapping[f'blk.{l}.kv_cache.v'] = self.v_cache[l % self.n_kv]
+
+        if self.rope != "off":
+            from ..workloads import build_rope_cache
+            rope_type = int(self.metadata.get('rope_type', 0))
+            width = int(self.metadata.get('rotary_dim', self.D)) if rope_type == 2 else self.D
+            cos, sin = build_rope_cache(self.S, width, float(rope_theta))
+            self.rope_cos = A(cos.nbytes, "rope_cos", MemoryRegion.ACTIVATIONS)
+            self.rope_sin = A(sin.nbytes, "rope_sin", MemoryRegion.ACTIVATIONS)
+            hip.safe_memcpy_host_to_device(ctypes.c_void_p(self.rope_cos.ptr), cos, "rope_cos upload")
+            hip.safe_memcpy_host_to_device(ctypes.c_void_p(self.rope_sin.ptr), sin, "rope_sin upload")
+            self.tensor_mapping['rope_cos'] = self.rope_cos
+            self.tensor_mapping['rope_sin'] = self.rope_sin
 
         # pinned staging: offsets, a step's Q, a step's outputs
         self._stage_offsets = hip.host_alloc(4 * self.B)
@@ -150,6 +172,9 @@ class DecodeAttentionExecutor:
             launches = self.dispatcher.build_launches(l, self.tensor_mapping, self.offsets.ptr, batch=self.B)
             if not self.with_append:
                 launches = launches[1:]
+            if self.rope == "separate":
+                launches = [self.dispatcher.build_rope_launch(self.tensor_mapping, self.offsets.ptr, batch=self.B,
+                                                              layer_idx=l)] + launches
             for fn, args, grid, block, smem in launches:
                 self.hip.launch_kernel_recorded(fn, args, grid, block, smem)
                 n += 1
@@ -165,6 +190,7 @@ class DecodeAttentionExecutor:
         try:
             if not self.use_graph:
                 n = len(self.dispatcher.build_launches(0, self.tensor_mapping, self.offsets.ptr, batch=self.B))
+                n += 1 if self.rope == "separate" else 0
                 self.kernel_launches_per_step = (n if self.with_append else n - 1) * self.L
                 return
             self.hip.stream_begin_capture()

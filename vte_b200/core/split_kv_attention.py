@@ -81,7 +81,7 @@ class SplitKVAttentionDispatcher:
                  batch_size: int = 1, *, num_splits: int | None = None, fixed_chunk_size=None,
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
                  strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True,
-                 fused_combine: bool | None = None, variant: str = "full"):
+                 fused_combine: bool | None = None, variant: str = "full", fuse_rope: bool = False):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -156,6 +156,23 @@ class SplitKVAttentionDispatcher:
                          if (self.batch_size > 1 and not self.fixed_chunk) else 0)
         self.min_chunk = int(min_chunk)
 
+        # fuse_rope: q_name / k_name are the UN-rotated projections; the append launch rotates the K
+        # row as it enters the cache and the split launch rotates Q as it loads it, which removes the
+        # standalone rotation launch from the layer.  Tables come from tensor_mapping['rope_cos'] /
+        # ['rope_sin'] (vte/core/kernel_arg_builder.py:394-395), type and width from the metadata keys
+        # `rope_type` / `rotary_dim` (:401-406).  The reference tried this fusion and took it out again
+        # (docs/PERFORMANCE.md, "RoPE fusion into Split-KV attention").
+        self.fuse_rope = bool(fuse_rope)
+        self.rope_type = int(self.metadata.get('rope_type', 0))
+        self.rotary_dim = int(self.metadata.get('rotary_dim', self.head_dim))
+        if self.fuse_rope:
+            if self.compat or self.lite:
+                raise CudaSafetyError("fuse_rope needs the full-shape fast kernels")
+            if self.rope_type not in (0, 1, 2):
+                raise CudaSafetyError(f"rope_type {self.rope_type} not in 0, 1, 2")
+            if self.rope_type == 2 and (self.rotary_dim not in (32, 64, 128, 256) or self.rotary_dim > self.head_dim):
+                raise CudaSafetyError(f"rotary_dim {self.rotary_dim} must be 32, 64, 128 or 256 and at most head_dim")
+
         self._kernel_cache = {}
         self._rows_combine = False
         self._partial_m = self._partial_l = self._partial_o = self._work = None
@@ -195,7 +212,8 @@ class SplitKVAttentionDispatcher:
             arch = self.hip.get_gpu_architecture()
             params = {'split_kv_chunk_size': self.chunk_size} if self.fixed_chunk else {}
             load = lambda template, symbol: self.codegen.load_kernel_safe(self.hip, template, arch, symbol, **params)[1]
-            self._kernel_cache['append'] = load('kv_cache_append', 'kv_cache_append_kernel')
+            self._kernel_cache['append'] = load(
+                'kv_cache_append', 'kv_cache_append_rope_kernel' if self.fuse_rope else 'kv_cache_append_kernel')
             if self.compat:
                 self._kernel_cache['partial'] = load('flash_attention_split_kv_partial',
                                                      'flash_attention_split_kv_partial_kernel')
@@ -205,7 +223,8 @@ class SplitKVAttentionDispatcher:
                     else 'flash_attention_split_kv_reduce_kernel')
             else:
                 self._kernel_cache['partial'] = load(
-                    'decode_attention', f"vteb_split_kv_partial_{'lite_' if self.lite else ''}d{self.head_dim}_kernel")
+                    'decode_attention',
+                    f"vteb_split_kv_partial_{'lite_' if self.lite else 'rope_' if self.fuse_rope else ''}d{self.head_dim}_kernel")
                 # short split lists (batched decode): one warp per (sequence, head) row;
                 # long ones (one sequence spread over every SM): one CTA per 32 columns
                 self._rows_combine = self.max_chunks <= 64
@@ -227,6 +246,29 @@ class SplitKVAttentionDispatcher:
             if hasattr(self.hip, 'safe_memset'):
                 self.hip.safe_memset(ctypes.c_void_p(self._work.ptr), 16, "attn_splitkv_work")
         return self._kernel_cache['append'], self._kernel_cache['partial'], self._kernel_cache['reduce']
+
+    def build_rope_launch(self, tensor_mapping: dict, kv_offset_ptr: int, batch: int = 1,
+                          q_name: str = None, k_name: str = None, layer_idx: int = 0, block_size: int = 256):
+        """The standalone rotation launch of one decode step, for callers that keep it separate:
+        `rope_kernel` with the reference's eleven arguments (vte/core/kernel_arg_builder.py:388-431)
+        and its grid rule (ceil(elements of Q / block) blocks in x, batch in y;
+        vte/core/hip_graph_executor.py:359-367).  Rotates Q and K in place."""
+        arch = self.hip.get_gpu_architecture()
+        if 'rope' not in self._kernel_cache:
+            self._kernel_cache['rope'] = self.codegen.load_kernel_safe(self.hip, 'rope', arch, 'rope_kernel')[1]
+        q_ptr = self._resolve_ptr(tensor_mapping, q_name or f'blk.{layer_idx}.q_proj.output')
+        k_ptr = self._resolve_ptr(tensor_mapping, k_name or f'blk.{layer_idx}.k_proj.output')
+        cos_ptr = self._resolve_ptr(tensor_mapping, 'rope_cos')
+        sin_ptr = self._resolve_ptr(tensor_mapping, 'rope_sin')
+        kv_offset_ptr = int(kv_offset_ptr.value or 0) if isinstance(kv_offset_ptr, ctypes.c_void_p) else int(kv_offset_ptr or 0)
+        for name, p in (("q", q_ptr), ("k", k_ptr), ("rope_cos", cos_ptr), ("rope_sin", sin_ptr), ("kv offsets", kv_offset_ptr)):
+            if not p:
+                raise CudaSafetyError(f"{name} pointer could not be resolved (null)")
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        args = [vp(q_ptr), vp(k_ptr), vp(cos_ptr), vp(sin_ptr), ci(1), ci(self.num_q_heads), ci(self.num_kv_heads),
+                ci(self.head_dim), vp(kv_offset_ptr), ci(self.rope_type), ci(self.rotary_dim)]
+        grid_x = max(1, -(-(self.num_q_heads * self.head_dim) // block_size))
+        return (self._kernel_cache['rope'], args, (grid_x, batch, 1), (block_size, 1, 1), 0)
 
     @property
     def work_ptr(self) -> int:
@@ -281,7 +323,14 @@ class SplitKVAttentionDispatcher:
         vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         append_args = [vp(k_proj_ptr), vp(v_proj_ptr), vp(k_cache_ptr), vp(v_cache_ptr),
                        ci(Hkv), ci(D), vp(kv_offset_ptr), ci(kv_batch_stride)]
-        append = (append_fn, append_args, (batch, Hkv, 1), (D, 1, 1), 0)
+        rope_tail = []
+        if self.fuse_rope:
+            cos_ptr = self._resolve_ptr(tensor_mapping, 'rope_cos')
+            sin_ptr = self._resolve_ptr(tensor_mapping, 'rope_sin')
+            if not cos_ptr or not sin_ptr or cos_ptr % 4 or sin_ptr % 4:
+                raise CudaSafetyError("fuse_rope: rope_cos / rope_sin missing from the tensor mapping or misaligned")
+            rope_tail = [vp(cos_ptr), vp(sin_ptr), ci(self.rope_type), ci(self.rotary_dim)]
+        append = (append_fn, append_args + rope_tail, (batch, Hkv, 1), (D, 1, 1), 0)
 
         reference_partial_args = [
             vp(q_ptr), vp(k_cache_ptr), vp(v_cache_ptr),
@@ -316,7 +365,7 @@ class SplitKVAttentionDispatcher:
         partial_args = reference_partial_args + [
             ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4),
             vp(next_k), vp(next_v),
-            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0)]
+            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0)] + rope_tail
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
         if self.fused_combine or direct:
             return [append, partial]

@@ -51,6 +51,82 @@ extern "C" __global__ void kv_cache_append_kernel(
 }
 
 // ---------------------------------------------------------------------------
+// kv_cache_append_rope_kernel: the append with the K rotation folded in, so the
+// row is rotated exactly once, where it enters the cache (rotating K on the
+// attention read would rotate history again every step).  Same grid and block;
+// `k` is the un-rotated projection and is left as it is.  The reference tried
+// this fusion together with the Q-side one of the split kernel and removed it
+// again; its standalone counterpart is rope_kernel below.
+// ---------------------------------------------------------------------------
+extern "C" __global__ void kv_cache_append_rope_kernel(
+    const __half* __restrict__ k, const __half* __restrict__ v,
+    __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+    int num_kv_heads, int head_dim,
+    const int* __restrict__ kv_cache_offset_ptr, int kv_batch_stride,
+    const __half* __restrict__ cos_cache, const __half* __restrict__ sin_cache,
+    int rope_type, int rotary_dim)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int b = blockIdx.x, head = blockIdx.y;
+    const int pos = kv_cache_offset_ptr[b];
+    const long long row = (long long)pos * num_kv_heads + head;
+    const long long dst = (long long)b * kv_batch_stride + row * head_dim;
+    const long long src = ((long long)b * num_kv_heads + head) * head_dim;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        k_cache[dst + d] = rope_channel(k + src, d, head_dim, cos_cache, sin_cache, pos, rope_type, rotary_dim);
+        v_cache[dst + d] = v[src + d];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// rope_kernel: in-place rotation of Q and K, any grid (gx, B, 1) and block.
+// Replaces vte/compiler/templates/rdna/rope.hip.template:17-140 with its
+// argument list: q [B, seq_len, Hq, D], k [B, seq_len, Hkv, D], token i of
+// sequence b sits at position kv_cache_offset_ptr[b] + i.  One thread per
+// rotated pair (grid-stride over the pairs of Q, then of K).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void rope_rows_inplace(__half* x, int seq_len, int heads, int D, int pos0,
+                                                  const __half* cos_cache, const __half* sin_cache,
+                                                  int rope_type, int rotary_dim)
+{
+    const int rot = (rope_type == 1 || rope_type == 0) ? D : rotary_dim;
+    const int pairs_per_row = rot >> 1;
+    const long long n_pairs = (long long)seq_len * heads * pairs_per_row;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        const long long rowi = p / pairs_per_row;
+        const int j = (int)(p - rowi * pairs_per_row);
+        const int pos = pos0 + (int)(rowi / heads);
+        __half* row = x + rowi * D;
+        const int i1 = (rope_type == 1) ? 2 * j : j;
+        const int i2 = (rope_type == 1) ? 2 * j + 1 : j + pairs_per_row;
+        const long long tab = (long long)pos * rot + j;
+        float y1, y2;
+        rope_pair(__half2float(row[i1]), __half2float(row[i2]),
+                  __half2float(cos_cache[tab]), __half2float(sin_cache[tab]), y1, y2);
+        row[i1] = __float2half(y1);
+        row[i2] = __float2half(y2);
+    }
+}
+
+extern "C" __global__ void rope_kernel(
+    __half* __restrict__ q, __half* __restrict__ k,
+    const __half* __restrict__ cos_cache, const __half* __restrict__ sin_cache,
+    int seq_len, int num_q_heads, int num_kv_heads, int head_dim,
+    const int* __restrict__ kv_cache_offset_ptr, int rope_type, int rotary_dim)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int b = blockIdx.y;
+    const int pos0 = kv_cache_offset_ptr[b];
+    rope_rows_inplace(q + (long long)b * seq_len * num_q_heads * head_dim, seq_len, num_q_heads, head_dim, pos0,
+                      cos_cache, sin_cache, rope_type, rotary_dim);
+    rope_rows_inplace(k + (long long)b * seq_len * num_kv_heads * head_dim, seq_len, num_kv_heads, head_dim, pos0,
+                      cos_cache, sin_cache, rope_type, rotary_dim);
+}
+
+// ---------------------------------------------------------------------------
 // flash_attention_split_kv_partial_kernel, reference geometry:
 // grid (B, Hq, C), block (D, 1, 1) with D a multiple of 32 and at most 256.
 // Replaces flash_attention_split_kv_partial.hip.template:31-120.  Each warp

@@ -37,6 +37,8 @@ struct FastArgs {
     int batch, min_chunk, flags; const int* seq_order; int* ticket; int* status;
     const __half* next_k_cache; const __half* next_v_cache;   // optional: the next layer's caches, for L2 prefetch
     void* output; int out_kind;   // out_kind != 0: combine inside this launch (1 fp16, 2 fp32, 3 shard state)
+    // rotary tables for the kernels that rotate Q while loading it (null otherwise)
+    const __half* rope_cos; const __half* rope_sin; int rope_type, rotary_dim;
 };
 
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
@@ -182,7 +184,7 @@ __device__ __forceinline__ ItemGeometry decode_item(const FastArgs& a, const Fas
     return g;
 }
 
-template <int D, int CW>
+template <int D, int CW, bool kRope = false>
 __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 {
     constexpr bool kLite = (CW == kLiteConsumerWarps);
@@ -388,6 +390,12 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         for (int ks = 0; ks < KS; ++ks) {
             tmp[2 * ks] = (g < group) ? qrow[ks * 8 + t] : 0u;
             tmp[2 * ks + 1] = (g < group) ? qrow[ks * 8 + 4 + t] : 0u;
+        }
+        if constexpr (kRope) {
+            // q holds the un-rotated projection: rotate it at the sequence's current position, in
+            // fp32, and round to fp16 exactly as the standalone rotation kernel would have stored it
+            if (g < group)
+                rope_rotate_q_words<KS>(tmp, a.rope_cos, a.rope_sin, a.kv_offsets[b], a.rope_type, a.rotary_dim, t);
         }
 #pragma unroll
         for (int i = 0; i < KS * 2; ++i) q_frag[i * 32] = tmp[i];
@@ -712,8 +720,40 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.seq_order = seq_order; a.ticket = ticket; a.status = status;                                \
         a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
         a.output = output; a.out_kind = out_kind;                                                     \
+        a.rope_cos = nullptr; a.rope_sin = nullptr; a.rope_type = 0; a.rotary_dim = 0;                \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM, CWARPS>(a);                                                            \
+    }
+
+// The same kernel with the Q rotation folded into the Q load: `q` is the un-rotated projection,
+// four more arguments name the tables (fp16 [max_seq, head_dim], or [max_seq, rotary_dim] for
+// rope_type 2), the rotation type and the rotated width.
+#define VTEB_FAST_PARTIAL_ROPE(NAME, DIM)                                                             \
+    extern "C" __global__ void __launch_bounds__(kFullThreads, 1) NAME(                               \
+        const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
+        const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
+        float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
+        int num_kv_heads, int head_dim, float scale, const int* __restrict__ kv_cache_offset_ptr,     \
+        int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
+        const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status,        \
+        const __half* __restrict__ next_k_cache, const __half* __restrict__ next_v_cache,             \
+        void* __restrict__ output, int out_kind,                                                      \
+        const __half* __restrict__ cos_cache, const __half* __restrict__ sin_cache,                   \
+        int rope_type, int rotary_dim)                                                                \
+    {                                                                                                 \
+        FastArgs a;                                                                                   \
+        a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
+        a.partial_m = partial_m; a.partial_l = partial_l; a.partial_o = partial_o;                    \
+        a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.scale = scale;                  \
+        a.kv_offsets = kv_cache_offset_ptr; a.kv_batch_stride = kv_batch_stride;                      \
+        a.max_chunks = max_chunks; a.batch = batch; a.min_chunk = min_chunk; a.flags = flags;         \
+        a.seq_order = seq_order; a.ticket = ticket; a.status = status;                                \
+        a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
+        a.output = output; a.out_kind = out_kind;                                                     \
+        a.rope_cos = cos_cache; a.rope_sin = sin_cache; a.rope_type = rope_type;                      \
+        a.rotary_dim = rotary_dim;                                                                    \
+        (void)head_dim;                                                                               \
+        fast_partial_body<DIM, kFullConsumerWarps, true>(a);                                          \
     }
 
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64, kFullConsumerWarps, kFullThreads, 1)
@@ -721,3 +761,6 @@ VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128, kFullConsumerWarps, kF
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256, kFullConsumerWarps, kFullThreads, 1)
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_lite_d64_kernel, 64, kLiteConsumerWarps, kLiteThreads, kLiteCtasPerSm)
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_lite_d128_kernel, 128, kLiteConsumerWarps, kLiteThreads, kLiteCtasPerSm)
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d64_kernel, 64)
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d128_kernel, 128)
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d256_kernel, 256)

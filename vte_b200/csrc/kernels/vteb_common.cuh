@@ -256,6 +256,92 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// ---- rotary position embedding --------------------------------------------
+// One rotated pair, as vte/compiler/templates/rdna/rope.hip.template:62-63,76-77,94-95
+// writes it: y1 = x1*c - x2*s, y2 = x1*s + x2*c in fp32.  Every product is rounded on
+// its own (no fused multiply-add), so the standalone kernel, the rotation fused into
+// the cache append and the one fused into the split kernel's Q load give identical bits.
+__device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, float& y1, float& y2) {
+    y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+    y2 = __fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c));
+}
+
+__device__ __forceinline__ float2 unpack_half2(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+// Split-half rotation of a lane's Q operand words when the rotated width is HK * 32
+// channels: word q[2*ks + e] (k-step ks, e = 0/1) holds channels ks*16 + e*8 + 2t, +1 and
+// pairs with the same word HK k-steps later.  `c32`/`s32` point at the position's table row.
+template <int KS, int HK>
+__device__ __forceinline__ void rope_rotate_words_split_half(uint32_t (&q)[KS * 2], const uint32_t* c32,
+                                                             const uint32_t* s32, int t) {
+#pragma unroll
+    for (int ks = 0; ks < HK; ++ks) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int w = ks * 8 + e * 4 + t;
+            const float2 c = unpack_half2(c32[w]), s = unpack_half2(s32[w]);
+            const float2 lo = unpack_half2(q[2 * ks + e]), hi = unpack_half2(q[2 * (ks + HK) + e]);
+            float a0, b0, a1, b1;
+            rope_pair(lo.x, hi.x, c.x, s.x, a0, b0);
+            rope_pair(lo.y, hi.y, c.y, s.y, a1, b1);
+            q[2 * ks + e] = pack_half2(a0, a1);
+            q[2 * (ks + HK) + e] = pack_half2(b0, b1);
+        }
+    }
+}
+
+// Rotates a lane's Q operand words (layout above) at position `pos`.
+// rope_type 0: split-half over the head, table rows of KS*16 entries; 1: adjacent pairs,
+// entry i of a KS*16-entry row for pair (2i, 2i+1); 2: split-half over the first
+// `rotary_dim` channels (32, 64, 128 or 256), table rows of rotary_dim entries.
+template <int KS>
+__device__ __forceinline__ void rope_rotate_q_words(uint32_t (&q)[KS * 2], const __half* cos_table,
+                                                    const __half* sin_table, int pos, int rope_type,
+                                                    int rotary_dim, int t) {
+    constexpr int D = KS * 16;
+    if (rope_type == 1) {
+        const __half* c = cos_table + (long long)pos * D;
+        const __half* s = sin_table + (long long)pos * D;
+#pragma unroll
+        for (int i = 0; i < KS * 2; ++i) {
+            const int w = (i >> 1) * 8 + (i & 1) * 4 + t;          // word index = pair index
+            const float2 x = unpack_half2(q[i]);
+            float y0, y1;
+            rope_pair(x.x, x.y, __half2float(c[w]), __half2float(s[w]), y0, y1);
+            q[i] = pack_half2(y0, y1);
+        }
+        return;
+    }
+    const int rot = (rope_type == 2) ? rotary_dim : D;
+    const uint32_t* c32 = reinterpret_cast<const uint32_t*>(cos_table + (long long)pos * rot);
+    const uint32_t* s32 = reinterpret_cast<const uint32_t*>(sin_table + (long long)pos * rot);
+    const int hk = rot >> 5;                                        // k-steps per rotated half
+    if (hk == 1) rope_rotate_words_split_half<KS, 1>(q, c32, s32, t);
+    if constexpr (KS >= 4) { if (hk == 2) rope_rotate_words_split_half<KS, 2>(q, c32, s32, t); }
+    if constexpr (KS >= 8) { if (hk == 4) rope_rotate_words_split_half<KS, 4>(q, c32, s32, t); }
+    if constexpr (KS >= 16) { if (hk == 8) rope_rotate_words_split_half<KS, 8>(q, c32, s32, t); }
+}
+
+// One channel of a rotated row: what channel `d` of the D-wide row `x` becomes.
+__device__ __forceinline__ __half rope_channel(const __half* x, int d, int D, const __half* cos_table,
+                                               const __half* sin_table, int pos, int rope_type, int rotary_dim) {
+    float y1, y2;
+    if (rope_type == 1) {
+        const int i = d >> 1;
+        rope_pair(__half2float(x[2 * i]), __half2float(x[2 * i + 1]),
+                  __half2float(cos_table[(long long)pos * D + i]), __half2float(sin_table[(long long)pos * D + i]), y1, y2);
+        return __float2half((d & 1) ? y2 : y1);
+    }
+    const int rot = (rope_type == 2) ? rotary_dim : D;
+    if (d >= rot) return x[d];
+    const int half = rot >> 1, j = (d < half) ? d : d - half;
+    rope_pair(__half2float(x[j]), __half2float(x[j + half]),
+              __half2float(cos_table[(long long)pos * rot + j]), __half2float(sin_table[(long long)pos * rot + j]), y1, y2);
+    return __float2half((d < half) ? y1 : y2);
+}
+
 #endif  // __CUDACC__
 
 }  // namespace vteb

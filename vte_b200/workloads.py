@@ -108,6 +108,18 @@ def rope_rotate_neox(x: np.ndarray, position: int, theta: float) -> np.ndarray:
     return np.concatenate([lo * cos - hi * sin, lo * sin + hi * cos], axis=-1).astype(np.float16)
 
 
+def build_rope_cache(max_seq_len: int, width: int, theta: float):
+    """fp16 cos and sin tables [max_seq_len, width], both halves of a row equal, with the
+    reference's arithmetic (fp32 positions times fp32 inverse frequencies
+    theta^-(i / (width/2)); vte/compiler/rope_cache_builder.py:58-90).  `width` is head_dim,
+    or rotary_dim for the partial rotation (vte/compiler/qwen3_5_mapper.py:292-298)."""
+    half = width // 2
+    inv_freq = 1.0 / (theta ** (np.arange(0, half, dtype=np.float32) / half))
+    ang = np.outer(np.arange(max_seq_len, dtype=np.float32), inv_freq)
+    cos_h, sin_h = np.cos(ang).astype(np.float16), np.sin(ang).astype(np.float16)
+    return np.concatenate([cos_h, cos_h], axis=1), np.concatenate([sin_h, sin_h], axis=1)
+
+
 def make_layer_inputs(cfg: DecodeConfig, layer: int = 0, lengths: np.ndarray | None = None,
                       seq_slice: slice | None = None):
     """(q [B,Hq,D] f16, k_cache [B,max_seq,Hkv,D] f16, v_cache, kv_offsets int32[B]).
