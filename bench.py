@@ -321,7 +321,7 @@ def run_ours(args, rank, world, local_rank):
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
                                    "programmatic_dependent_launch": not args.no_pdl,
                                    "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1,
-                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, lite CTAs" if ex.dispatcher.lite else "fast, full CTAs"),
+                                   "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, compact CTAs" if ex.dispatcher.compact else "fast, full CTAs"),
                                    "step_contents": {"off": "split + combine per layer",
                                                      "separate": "rotation launch + cache append + split + combine per layer",
                                                      "fused": "cache append with K rotation + split with Q rotation + combine per layer"}[args.rope]}),
@@ -446,7 +446,7 @@ def kernel_durations(rt, ex, n_layers, reps=10):
     includes the in-graph launch gap between consecutive kernels."""
     disp = ex.dispatcher
     name = ("flash_attention_split_kv_partial_kernel" if disp.compat else
-            f"vteb_split_kv_partial_{'lite_' if disp.lite else 'rope_' if disp.fuse_rope else ''}d{disp.head_dim}_kernel")
+            f"vteb_split_kv_partial_{'compact_' if disp.compact else ''}{'rope_' if disp.fuse_rope else ''}d{disp.head_dim}_kernel")
     out = {}
     kinds = ((0, "split_us"),) if disp.fused_combine else ((0, "split_us"), (1, "combine_us"))
     out["combine_us"] = 0.0
@@ -503,7 +503,7 @@ def main():
                     help="sequences partition: give each rank the same number of sequences but pick them "
                          "longest-first onto the least loaded rank instead of contiguous blocks")
     ap.add_argument("--no-pdl", action="store_true")
-    ap.add_argument("--variant", default="full", choices=["full", "lite"], help="CTA shape of the split kernel")
+    ap.add_argument("--variant", default="auto", choices=["full", "compact", "auto"], help="CTA shape of the split kernel")
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")

@@ -150,9 +150,11 @@ typedef struct vteb_fast_plan {
     int combine_smem_bytes; /* per split, up to 256 splits: min(max_chunks, 256) * this */
 } vteb_fast_plan;
 int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
-/* Same for the small CTA shape (4 consumer warps + 1 loader warp, one KV head per item,
- * three CTAs per SM) used when one launch gives every SM well under a megabyte. */
-int vteb_split_kv_plan_lite(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
+/* Same for the compact CTA shape (4 consumer warps + 2 loader warps, still one CTA per
+ * SM): it leaves register-file room beside it for the CTAs of the combine launch, which
+ * shortens a layer whose whole split launch lasts only some microseconds.  `ok` is 0 when
+ * a head group needs more than four consumer warps. */
+int vteb_split_kv_plan_compact(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
 /* Columns per lane of the short-list combine kernel (split counts up to 64): a warp
  * merges 32 * epl columns of one (sequence, head) row. */
 int vteb_combine_rows_epl(int rows, int head_dim);
@@ -175,7 +177,7 @@ int vteb_combine_rows_epl(int rows, int head_dim);
 #define VTEB_ATTN_COMPAT 1
 #define VTEB_ATTN_WRITE_EMPTY_O 2
 #define VTEB_ATTN_PROGRAMMATIC 4
-#define VTEB_ATTN_LITE 16   /* small CTA shape, see vteb_split_kv_plan_lite */
+#define VTEB_ATTN_COMPACT 16   /* compact CTA shape where it applies, see vteb_split_kv_plan_compact */
 int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache,
                          const int* kv_offsets, void* output, int out_is_f32,
                          float* partial_m, float* partial_l, float* partial_o, int* work,

@@ -49,11 +49,11 @@ def test_plan_is_pure_host_arithmetic(built_library):
         assert plan.ok == 1 and plan.hg == hg and plan.n_hgroups == nhg
         assert plan.smem_bytes <= 227 * 1024 and plan.nstages >= 2 and plan.tile % 16 == 0
         assert plan.threads == 320 and plan.combine_dsplit == d // 32
-        lite = FastPlan()
-        assert lib.vteb_split_kv_plan_lite(hq, hkv, d, ctypes.byref(lite)) == 0
-        assert lite.ok == (0 if d == 256 else 1)
-        if lite.ok:
-            assert lite.threads == 160 and lite.hg == 1 and lite.smem_bytes <= 74 * 1024 and lite.nstages >= 2
+        small = FastPlan()
+        assert lib.vteb_split_kv_plan_compact(hq, hkv, d, ctypes.byref(small)) == 0
+        if small.ok:
+            assert small.threads == 192 and small.hg <= 4 and small.smem_bytes <= 227 * 1024 and small.nstages >= 2
+            assert small.hg * (2 if d == 256 else 1) <= 4
     for hq, hkv, d in [(32, 2, 128), (12, 2, 96), (12, 5, 128), (12, 0, 128)]:   # group 16, odd dim, non-divisor
         plan = FastPlan()
         assert lib.vteb_split_kv_plan(hq, hkv, d, ctypes.byref(plan)) == 0
@@ -90,9 +90,9 @@ class FakeRuntime:
     def get_num_cus(self): return self.sms
     def get_gpu_architecture(self): return "sm_100a"
     def combine_rows_epl(self, rows, d): return self._lib.vteb_combine_rows_epl(rows, d)
-    def split_kv_plan(self, hq, hkv, d, lite=False):
+    def split_kv_plan(self, hq, hkv, d, compact=False):
         plan = FastPlan()
-        (self._lib.vteb_split_kv_plan_lite if lite else self._lib.vteb_split_kv_plan)(hq, hkv, d, ctypes.byref(plan))
+        (self._lib.vteb_split_kv_plan_compact if compact else self._lib.vteb_split_kv_plan)(hq, hkv, d, ctypes.byref(plan))
         return plan
     def safe_malloc(self, n, tag="x"):
         p = self._next
@@ -134,8 +134,8 @@ def mapping(layer=0, stride=32768 * 2 * 128):
 
 # ----------------------------------------------------------------------------- dispatcher
 def test_fast_launch_list_shapes_and_signatures():
-    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, fused_combine=False)
-    assert d.enabled and not d.compat and d.max_chunks == 148 and not d.lite
+    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, fused_combine=False, variant="full")
+    assert d.enabled and not d.compat and d.max_chunks == 148 and not d.compact
     launches = d.build_launches(0, mapping(), 0x7200_0000_0000, batch=1)
     assert len(launches) == 3
     (fa, aa, ga, ba, sa), (fp, ap, gp, bp, sp), (fr, ar, gr, br, sr) = launches
@@ -195,10 +195,13 @@ def test_fused_rope_launch_list_and_standalone_rotation_launch():
     assert grid == (8 * 256 // 256, 4, 1) and block == (256, 1, 1) and smem == 0
     assert [a.value for a in args[4:8]] == [1, 8, 2, 256] and [a.value for a in args[9:]] == [2, 64]
     # options the rotation cannot be combined with, and widths the kernel has no code for
-    for kw in ({'compat': True}, {'variant': 'lite'}):
-        meta128 = {'attention.head_count': 12, 'attention.head_count_kv': 2, 'attention.key_length': 128}
-        with pytest.raises(CudaSafetyError):
-            make_dispatcher(meta128, fuse_rope=True, **kw)
+    meta128 = {'attention.head_count': 12, 'attention.head_count_kv': 2, 'attention.key_length': 128}
+    with pytest.raises(CudaSafetyError):
+        make_dispatcher(meta128, fuse_rope=True, compat=True)
+    dc, rtc, *_ = make_dispatcher(meta128, fuse_rope=True, context_length=4096)           # one sequence: compact shape
+    m128 = dict(mapping(), rope_cos=0x7300_0000_0000, rope_sin=0x7300_1000_0000)
+    assert dc.compact and len(dc.build_launches(0, m128, 0x7200_0000_0000)[1][1]) == 27
+    assert rtc.loaded[1][1] == "vteb_split_kv_partial_compact_rope_d128_kernel"
     with pytest.raises(CudaSafetyError):
         make_dispatcher(dict(meta, rotary_dim=48), fuse_rope=True)
     with pytest.raises(CudaSafetyError):
@@ -216,19 +219,26 @@ def test_rope_cache_builder_matches_the_pinned_tables():
         assert np.array_equal(cos[:, :width // 2], cos[:, width // 2:])
 
 
-def test_lite_shape_is_opt_in():
-    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, variant="lite")
-    assert d.lite and d.max_chunks == 148
-    (_, _, _, _, _), (fp, ap, gp, bp, sp), _ = d.build_launches(0, mapping(), 0x7200_0000_0000)
-    assert gp == (296, 1, 1) and bp == (160, 1, 1) and sp <= 74 * 1024
-    assert [s for _, s in rt.loaded][1] == "vteb_split_kv_partial_lite_d128_kernel"
-    default, *_ = make_dispatcher(context_length=32768, batch_size=1)
-    assert not default.lite
-    wide, *_ = make_dispatcher({'attention.head_count': 8, 'attention.head_count_kv': 2, 'attention.key_length': 256},
-                               variant="lite")
-    assert not wide.lite                                            # no lite kernel for 256-wide heads
+def test_compact_shape_selection():
+    d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, variant="compact")
+    assert d.compact and d.max_chunks == 148
+    fp, ap, gp, bp, sp = d.build_launches(0, mapping(), 0x7200_0000_0000, batch=1)[1]
+    assert gp == (148, 1, 1) and bp == (192, 1, 1) and 100_000 < sp <= 227 * 1024
+    assert [s for _, s in rt.loaded][1] == "vteb_split_kv_partial_compact_d128_kernel"
+    # auto: compact for one sequence, full for a batch
+    assert make_dispatcher(context_length=32768, batch_size=1, variant="auto")[0].compact
+    assert not make_dispatcher(context_length=32768, batch_size=4, variant="auto")[0].compact
+    assert not make_dispatcher(context_length=1 << 20, batch_size=1)[0].compact          # auto is the default
+    # 256-wide heads have a compact kernel too (two KV heads x two column halves = four warps)
+    wide = make_dispatcher({'attention.head_count': 8, 'attention.head_count_kv': 2, 'attention.key_length': 256},
+                           variant="compact")[0]
+    assert wide.compact
+    # eight 64-wide KV heads: four per item in the compact shape, eight in the full one
+    many = make_dispatcher({'attention.head_count': 32, 'attention.head_count_kv': 8, 'attention.key_length': 64},
+                           variant="compact")[0]
+    assert many.compact and many._plan.hg == 4 and many._plan.n_hgroups == 2
     with pytest.raises(CudaSafetyError):
-        make_dispatcher(variant="tiny")
+        make_dispatcher(variant="lite")
 
 
 def test_compat_launch_list_is_the_reference_geometry():

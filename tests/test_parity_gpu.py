@@ -402,20 +402,20 @@ def test_one_million_context(cuda_runtime, codegen):
     assert np.max(np.abs(outs[0] - outs[1])) < 1e-5
 
 
-@pytest.mark.parametrize("name", ["ragged_d64", "group8_d128", "mha_d128"])
-def test_lite_cta_shape_matches(cuda_runtime, codegen, name):
-    """The opt-in small CTA shape (4 consumer warps + 1 loader warp, one KV head per item)."""
+@pytest.mark.parametrize("name", ["ragged_d64", "group8_d128", "mha_d128", "outlier_d256"])
+def test_compact_cta_shape_matches(cuda_runtime, codegen, name):
+    """The compact CTA shape (4 consumer warps + 2 loader warps)."""
     cfg, lens = SMALL_CASES[name]
     q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
     ref = orc.decode_attention(q, k, v, off)
     for splits in (1, 5):
         out, (pm, pl, po), C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=splits, min_chunk=0,
-                                         variant="lite", strict_empty_splits=True)
+                                         variant="compact", strict_empty_splits=True)
         assert_parity(out, ref)
         assert_parity(orc.split_kv_reduce(pm, pl, po), ref)
     cfg = CONFIGS["c2"]
     q, k, v, off = make_layer_inputs(cfg, 0)
-    out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, variant="lite")
+    out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, variant="compact")
     assert_parity(out, np.load(GOLD / "attn_c2_layer0.npz")["out"], tight=2e-5)
 
 

@@ -34,11 +34,11 @@ CASES = {
 }
 
 
-def run_steps(rt, codegen, cfg, meta, mode, layers, news, offsets_per_step, splits):
+def run_steps(rt, codegen, cfg, meta, mode, layers, news, offsets_per_step, splits, variant):
     """Runs the decode steps in `mode` and returns, per step, (outputs [L,B,Hq,D], last cache rows of
     layer 0 per sequence, the Q buffer after the step)."""
     ex = DecodeAttentionExecutor(rt, codegen, meta, cfg.batch, cfg.max_seq, N_LAYERS, rope=mode, rope_theta=THETA,
-                                 num_splits=splits, min_chunk=0)
+                                 num_splits=splits, min_chunk=0, variant=variant)
     results = []
     try:
         for l, (q, k, v, _) in enumerate(layers):
@@ -72,8 +72,8 @@ def test_rotation_modes_match_oracle_and_each_other(cuda_runtime, codegen, name)
               rng.standard_normal((cfg.batch, Hkv, D), dtype=np.float32).astype(np.float16))
              for _ in range(N_LAYERS)] for _ in offsets_per_step]
 
-    for splits in (1, 4):
-        got = {mode: run_steps(cuda_runtime, codegen, cfg, meta, mode, layers, news, offsets_per_step, splits)
+    for splits, variant in ((1, "full"), (4, "full"), (3, "compact")):
+        got = {mode: run_steps(cuda_runtime, codegen, cfg, meta, mode, layers, news, offsets_per_step, splits, variant)
                for mode in ("separate", "fused")}
         caches = [(k.copy(), v.copy()) for _, k, v, _ in layers]
         for step, off in enumerate(offsets_per_step):
@@ -100,7 +100,7 @@ def test_rotation_modes_match_oracle_and_each_other(cuda_runtime, codegen, name)
                         else:
                             assert np.array_equal(q_after, q)              # left as it was
             # the two routes round at the same points: identical output bits
-            assert np.array_equal(got["separate"][step][0], got["fused"][step][0]), (splits, step)
+            assert np.array_equal(got["separate"][step][0], got["fused"][step][0]), (splits, variant, step)
 
 
 def test_rotation_kernel_handles_several_tokens_and_any_grid(cuda_runtime, codegen):

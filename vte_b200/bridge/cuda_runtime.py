@@ -46,7 +46,7 @@ LAUNCH_PROGRAMMATIC = 1
 ATTN_COMPAT = 1
 ATTN_WRITE_EMPTY_O = 2
 ATTN_PROGRAMMATIC = 4
-ATTN_LITE = 16
+ATTN_COMPACT = 16
 
 ERR_DEVICE_STATUS = -6
 
@@ -120,7 +120,7 @@ def _declare(lib):
         "vteb_ipc_open_handle": (i, [vp, vpp]),
         "vteb_ipc_close_handle": (i, [vp]),
         "vteb_split_kv_plan": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
-        "vteb_split_kv_plan_lite": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
+        "vteb_split_kv_plan_compact": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
         "vteb_combine_rows_epl": (i, [i, i]),
         "vteb_split_kv_decode": (i, [vp, vp, vp, vp, vp, i, vp, vp, vp, vp, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_split_kv_decode_noalloc": (i, [vp, vp, vp, vp, vp, i, i, i, i, i, f, ll, i, i, u, i, vp]),
@@ -639,9 +639,9 @@ class CudaRuntime:
         self._check_error(self._lib.vteb_ipc_close_handle(ctypes.c_void_p(_ptr_value(ptr))), "cudaIpcCloseMemHandle")
 
     # ------------------------------------------------------------------ attention entry points
-    def split_kv_plan(self, num_q_heads: int, num_kv_heads: int, head_dim: int, lite: bool = False) -> FastPlan:
+    def split_kv_plan(self, num_q_heads: int, num_kv_heads: int, head_dim: int, compact: bool = False) -> FastPlan:
         plan = FastPlan()
-        fn = self._lib.vteb_split_kv_plan_lite if lite else self._lib.vteb_split_kv_plan
+        fn = self._lib.vteb_split_kv_plan_compact if compact else self._lib.vteb_split_kv_plan
         self._check_error(fn(num_q_heads, num_kv_heads, head_dim, ctypes.byref(plan)), "vteb_split_kv_plan")
         return plan
 

@@ -34,8 +34,12 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_partial_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL,
     "vteb_split_kv_partial_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL,
     "vteb_split_kv_partial_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL,
-    "vteb_split_kv_partial_lite_d64_kernel": _FAST_PARTIAL,
-    "vteb_split_kv_partial_lite_d128_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_compact_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL,
+    "vteb_split_kv_partial_compact_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL,
+    "vteb_split_kv_partial_compact_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL,
+    "vteb_split_kv_partial_compact_d64_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_compact_d128_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_compact_d256_kernel": _FAST_PARTIAL,
     "vteb_split_kv_combine_f16_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_f32_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_state_kernel": _FAST_COMBINE,

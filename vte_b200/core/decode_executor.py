@@ -32,7 +32,7 @@ class DecodeAttentionExecutor:
                  with_append: bool = False, fixed_chunk_size=None, min_chunk: Optional[int] = None,
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
                  emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
-                 fused_combine: Optional[bool] = None, variant: str = "full", rope: str = "off",
+                 fused_combine: Optional[bool] = None, variant: str = "auto", rope: str = "off",
                  rope_theta: float = 1e6):
         self.hip = hip
         # rope: "off" = Q and K arrive rotated; "separate" = the reference's standalone rotation

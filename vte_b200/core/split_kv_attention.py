@@ -32,6 +32,7 @@ MAX_SPLITS = 256
 TARGET_CHUNK_POSITIONS = 256      # smallest chunk length aimed at when many sequences share the GPU
 FLAG_WRITE_EMPTY_O = 1
 FLAG_DIRECT_OUTPUT = 2
+COMPACT_MAX_CONTEXT = 262144      # one sequence up to this long: the compact CTA shape (launches of tens of microseconds)
 UNSPLIT_MAX_CONTEXT = 128         # below this, one CTA per (sequence, head group) finishes before a combine could launch
 
 
@@ -81,7 +82,7 @@ class SplitKVAttentionDispatcher:
                  batch_size: int = 1, *, num_splits: int | None = None, fixed_chunk_size=None,
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
                  strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True,
-                 fused_combine: bool | None = None, variant: str = "full", fuse_rope: bool = False):
+                 fused_combine: bool | None = None, variant: str = "auto", fuse_rope: bool = False):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -103,21 +104,27 @@ class SplitKVAttentionDispatcher:
         num_cus = hip.get_num_cus() if hip is not None and hasattr(hip, 'get_num_cus') else 32
         self.num_sms = num_cus
 
-        # CTA shape of the split kernel.  "full": 8 + 2 warps, one CTA per SM.  "lite": 4 + 1 warps,
-        # one KV head per work item, three CTAs per SM, so that the next layer's launch can already
-        # be resident and loading under programmatic dependent launch.  Measured on B200 at 32k
-        # context: lite 17.0 us per layer, full 13.5 us (one loader warp and three stages do not
-        # keep the HBM stream up), so lite is opt-in.
-        if variant not in ("full", "lite"):
-            raise CudaSafetyError(f"variant must be full or lite, not {variant!r}")
+        # CTA shape of the split kernel.  "full": 8 consumer + 2 loader warps.  "compact": 4 + 2
+        # warps, which leaves register-file room on every SM for the combine launch's CTAs to sit
+        # beside the split CTA, so the combine starts the moment the split ends and the launch after
+        # it is not held back.  Measured on B200, 32k context, one sequence: 11.4 us per layer compact
+        # against 13.6 us full, 8.7 against 10.8 at 512 positions; batches of ragged sequences and a
+        # one-million-position sequence run 3 to 18 % slower compact (four warps do not keep up with
+        # a stream that lasts hundreds of microseconds).  "auto" therefore takes compact for one
+        # sequence of up to COMPACT_MAX_CONTEXT positions and full otherwise.
+        if variant not in ("full", "compact", "auto"):
+            raise CudaSafetyError(f"variant must be full, compact or auto, not {variant!r}")
         self._plan = None
-        self.lite = False
+        self.compact = False
         if hip is not None and hasattr(hip, 'split_kv_plan'):
             self._plan = hip.split_kv_plan(self.num_q_heads, self.num_kv_heads, self.head_dim)
-            if variant == "lite" and not self.compat:
-                lite_plan = hip.split_kv_plan(self.num_q_heads, self.num_kv_heads, self.head_dim, lite=True)
-                if lite_plan.ok:
-                    self._plan, self.lite = lite_plan, True
+            want_compact = variant == "compact" or (variant == "auto" and self.batch_size == 1
+                                                    and self.context_length <= COMPACT_MAX_CONTEXT
+                                                    and not fused_combine)
+            if want_compact and not self.compat:
+                compact_plan = hip.split_kv_plan(self.num_q_heads, self.num_kv_heads, self.head_dim, compact=True)
+                if compact_plan.ok:
+                    self._plan, self.compact = compact_plan, True
         if self.emit_state and (self.compat or self._plan is None or not self._plan.ok):
             raise CudaSafetyError("emit_state needs the fast kernels (group <= 8, head_dim 64/128/256)")
         if not self.compat and (self._plan is None or not self._plan.ok):
@@ -126,7 +133,7 @@ class SplitKVAttentionDispatcher:
 
         # fused_combine: the split launch also merges the splits (after a grid-wide barrier), so a
         # layer is append + ONE launch.  Needs all eight consumer warps (hg divides 8).
-        can_fuse = ((not self.compat) and (not self.lite) and self._plan is not None and self._plan.ok
+        can_fuse = ((not self.compat) and (not self.compact) and self._plan is not None and self._plan.ok
                     and 8 % self._plan.hg == 0)
         # Measured on B200 at 32k context: 15.1 us per layer fused against 13.4 us with the separate
         # combine launch (the grid barrier costs more than the launch it saves), so it is opt-in.
@@ -143,8 +150,6 @@ class SplitKVAttentionDispatcher:
             n_hg = self._plan.n_hgroups if (self._plan is not None and self._plan.ok) else self.num_kv_heads
             if num_splits:
                 self.max_chunks = int(num_splits)
-            elif self.lite and self.batch_size == 1:
-                self.max_chunks = max(1, min(MAX_SPLITS, num_cus))       # n_hgroups items per split: a few per SM
             else:
                 self.max_chunks = choose_split_count(num_cus, self.batch_size, n_hg, self.context_length)
             if not (1 <= self.max_chunks <= 65535):
@@ -166,8 +171,8 @@ class SplitKVAttentionDispatcher:
         self.rope_type = int(self.metadata.get('rope_type', 0))
         self.rotary_dim = int(self.metadata.get('rotary_dim', self.head_dim))
         if self.fuse_rope:
-            if self.compat or self.lite:
-                raise CudaSafetyError("fuse_rope needs the full-shape fast kernels")
+            if self.compat:
+                raise CudaSafetyError("fuse_rope needs the fast kernels")
             if self.rope_type not in (0, 1, 2):
                 raise CudaSafetyError(f"rope_type {self.rope_type} not in 0, 1, 2")
             if self.rope_type == 2 and (self.rotary_dim not in (32, 64, 128, 256) or self.rotary_dim > self.head_dim):
@@ -224,7 +229,7 @@ class SplitKVAttentionDispatcher:
             else:
                 self._kernel_cache['partial'] = load(
                     'decode_attention',
-                    f"vteb_split_kv_partial_{'lite_' if self.lite else 'rope_' if self.fuse_rope else ''}d{self.head_dim}_kernel")
+                    f"vteb_split_kv_partial_{'compact_' if self.compact else ''}{'rope_' if self.fuse_rope else ''}d{self.head_dim}_kernel")
                 # short split lists (batched decode): one warp per (sequence, head) row;
                 # long ones (one sequence spread over every SM): one CTA per 32 columns
                 self._rows_combine = self.max_chunks <= 64
@@ -346,7 +351,7 @@ class SplitKVAttentionDispatcher:
 
         plan = self._plan
         items = batch * plan.n_hgroups * C
-        n_ctas = max(1, min(items, self.num_sms * (3 if self.lite else 1)))
+        n_ctas = max(1, min(items, self.num_sms))
         flags = FLAG_WRITE_EMPTY_O if self.strict_empty_splits else 0
         next_k = next_v = 0
         if self.prefetch_next_layer:
@@ -358,7 +363,7 @@ class SplitKVAttentionDispatcher:
         # One split and an ordinary output: the split launch normalises and stores the attention
         # output itself (the reference's unsplit kernel, flash_attention.hip.template:29-113, in one
         # launch).  Needs one CTA per work item, because nothing resets the work queue afterwards.
-        direct = C == 1 and not self.emit_state and not self.strict_empty_splits and items <= self.num_sms * (3 if self.lite else 1)
+        direct = C == 1 and not self.emit_state and not self.strict_empty_splits and items <= self.num_sms
         if direct:
             flags |= FLAG_DIRECT_OUTPUT
         pass_output = self.fused_combine or direct

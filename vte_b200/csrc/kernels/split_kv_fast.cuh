@@ -1,12 +1,13 @@
 // Fast split kernel of the decode-attention path (included by decode_attention.cu).
 //
 // grid (n_ctas, 1, 1) persistent, block 320 = eight consumer warps + two loader
-// warps, dynamic shared memory from make_fast_plan().  A work item is one split
+// warps (192 = four + two in the compact shape), dynamic shared memory from
+// make_fast_plan().  A work item is one split
 // of one sequence for one group of `hg` KV heads; item t maps to
 // (sequence rank t / (n_hgroups * C), head group, split).  CTA i starts with
 // item i and draws the following ones from `*ticket` (gridDim.x + atomicAdd).
 //
-// Loader warp K (warp 8): for every tile of `tile` positions it waits for a free
+// Loader warp K (the first warp after the consumers): for every tile of `tile` positions it waits for a free
 // stage, writes the tile header, and copies the K rows (row_bytes contiguous
 // bytes covering the group's heads) with 16-byte asynchronous copies, one
 // 512-byte piece per warp instruction, into rows padded by 16 bytes.  Loader
@@ -187,11 +188,11 @@ __device__ __forceinline__ ItemGeometry decode_item(const FastArgs& a, const Fas
 template <int D, int CW, bool kRope = false>
 __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 {
-    constexpr bool kLite = (CW == kLiteConsumerWarps);
-    constexpr int kLoaderWarpK = CW;          // loads K rows (and V rows in the lite shape), owns the work queue
-    constexpr int kLoaderWarpV = CW + 1;      // full shape only: loads V rows, follows the K loader's headers
+    constexpr bool kCompact = (CW == kCompactConsumerWarps);
+    constexpr int kLoaderWarpK = CW;          // loads K rows, owns the work queue
+    constexpr int kLoaderWarpV = CW + 1;      // loads V rows, follows the K loader's headers
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const FastPlan plan = make_fast_plan(a.num_q_heads, a.num_kv_heads, D, kLite ? 1 : 0);
+    const FastPlan plan = make_fast_plan(a.num_q_heads, a.num_kv_heads, D, kCompact ? 1 : 0);
     const int group = a.num_q_heads / a.num_kv_heads;
 
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem_raw + kAbortOffset);
@@ -215,7 +216,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(full0 + 8 * s, kLite ? 33 : 65);   // asynchronous-copy arrivals of the loader lanes + the header writer
+            mbar_init(full0 + 8 * s, 65);   // asynchronous-copy arrivals of the loader lanes + the header writer
             mbar_init(empty0 + 8 * s, plan.active_warps);
             mbar_init(hdr0 + 8 * s, 1);
         }
@@ -281,12 +282,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     const unsigned char* src_last = src + (long long)(g.end - 1 - pos0) * pos_stride;
                     const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes);
                     copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
-                    if constexpr (kLite) {
-                        const long long k_to_v = reinterpret_cast<const unsigned char*>(a.v_cache) -
-                                                 reinterpret_cast<const unsigned char*>(a.k_cache);
-                        copy_rows_async(src + k_to_v, src_last + k_to_v, dst + plan.tile * plan.row_pitch, nrows, nvalid,
-                                        plan.row_bytes, plan.row_pitch, pos_stride, lane);
-                    }
                     async_copy_arrive(bar);
                 } else {
                     mbar_arrive(bar);      // no copies belong to this tile
@@ -310,18 +305,13 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                       2ll * (long long)g.b * a.kv_batch_stride + (long long)g.start * pos_stride,
                                   (long long)(g.end - g.start) * pos_stride, lane);
         }
-        if (kLite && a.next_v_cache != nullptr && plan.n_hgroups == 1 && total_items <= (int)gridDim.x &&
-            (int)blockIdx.x < total_items && first_geom.end > first_geom.start)
-            prefetch_range_l2(reinterpret_cast<const unsigned char*>(a.next_v_cache) +
-                                  2ll * (long long)first_geom.b * a.kv_batch_stride + (long long)first_geom.start * pos_stride,
-                              (long long)(first_geom.end - first_geom.start) * pos_stride, lane);
         if (!dep_done) grid_dependency_wait();
         asm volatile("cp.async.wait_all;" ::: "memory");   // own copies have landed before the warp leaves
         return;
     }
 
-    // ===================================================================== V loader (full shape)
-    if (!kLite && warp == kLoaderWarpV) {
+    // ===================================================================== V loader
+    if (warp == kLoaderWarpV) {
         int stage = 0;
         uint32_t hdr_parity = 0;
         bool dep_done = false;
@@ -671,7 +661,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
     }
 
-    if (kLite || a.out_kind == 0 || (a.flags & kFlagDirectOutput)) return;
+    if (kCompact || a.out_kind == 0 || (a.flags & kFlagDirectOutput)) return;
     // ===================================================================== in-launch combine
     // (needs all eight consumer warps; the host only asks for it then)
     // 1. every consumer warp's partial stores are fenced, then counted on a CTA barrier
@@ -700,8 +690,11 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         combine_slice<true>(a.partial_m, a.partial_l, a.partial_o, a.output, a.out_kind, D, a.max_chunks, dsplit, slice, merge);
 }
 
-#define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, THREADS, CTAS_PER_SM)                                    \
-    extern "C" __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) NAME(                          \
+// compact shape: the register cap is what leaves room for the combine launch's CTAs on the same SM
+#define VTEB_COMPACT_BOUNDS __maxnreg__(168)
+
+#define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, BOUNDS)                                                  \
+    extern "C" __global__ void BOUNDS NAME(                                                           \
         const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
         const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
         float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
@@ -728,8 +721,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 // The same kernel with the Q rotation folded into the Q load: `q` is the un-rotated projection,
 // four more arguments name the tables (fp16 [max_seq, head_dim], or [max_seq, rotary_dim] for
 // rope_type 2), the rotation type and the rotated width.
-#define VTEB_FAST_PARTIAL_ROPE(NAME, DIM)                                                             \
-    extern "C" __global__ void __launch_bounds__(kFullThreads, 1) NAME(                               \
+#define VTEB_FAST_PARTIAL_ROPE(NAME, DIM, CWARPS, BOUNDS)                                             \
+    extern "C" __global__ void BOUNDS NAME(                                                           \
         const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
         const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
         float* __restrict__ partial_l, float* __restrict__ partial_o, int num_q_heads,                \
@@ -753,14 +746,18 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.rope_cos = cos_cache; a.rope_sin = sin_cache; a.rope_type = rope_type;                      \
         a.rotary_dim = rotary_dim;                                                                    \
         (void)head_dim;                                                                               \
-        fast_partial_body<DIM, kFullConsumerWarps, true>(a);                                          \
+        fast_partial_body<DIM, CWARPS, true>(a);                                                      \
     }
 
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64, kFullConsumerWarps, kFullThreads, 1)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128, kFullConsumerWarps, kFullThreads, 1)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256, kFullConsumerWarps, kFullThreads, 1)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_lite_d64_kernel, 64, kLiteConsumerWarps, kLiteThreads, kLiteCtasPerSm)
-VTEB_FAST_PARTIAL(vteb_split_kv_partial_lite_d128_kernel, 128, kLiteConsumerWarps, kLiteThreads, kLiteCtasPerSm)
-VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d64_kernel, 64)
-VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d128_kernel, 128)
-VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d256_kernel, 256)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_compact_d64_kernel, 64, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_compact_d128_kernel, 128, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
+VTEB_FAST_PARTIAL(vteb_split_kv_partial_compact_d256_kernel, 256, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d64_kernel, 64, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d128_kernel, 128, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d256_kernel, 256, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_compact_rope_d64_kernel, 64, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_compact_rope_d128_kernel, 128, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
+VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_compact_rope_d256_kernel, 256, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)

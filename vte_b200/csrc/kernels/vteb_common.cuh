@@ -9,18 +9,20 @@
 
 namespace vteb {
 
-// Two shapes of the split kernel's CTA:
-//   full: 8 consumer warps + 2 loader warps (K rows / V rows), one CTA per SM, for work
-//         that keeps an SM busy for tens of microseconds;
-//   lite: 4 consumer warps + 1 loader warp, one KV head per work item, small enough that
-//         three CTAs share an SM, so that under programmatic dependent launch the next
-//         layer's CTAs are already resident and loading while this layer finishes.
+// Two shapes of the split kernel's CTA, both one CTA per SM with the whole shared memory
+// as K/V stages and two loader warps (K rows / V rows):
+//   full:    8 consumer warps, for work that keeps an SM busy for tens of microseconds;
+//   compact: 4 consumer warps.  Ten warps of 168 registers fill two of the SM's four
+//            register-file partitions, so no CTA of the combine kernel launched behind can
+//            become resident until a split CTA leaves, and the launch after that cannot
+//            even start until every combine CTA has.  Six warps leave room in every
+//            partition: the combine CTAs sit at their dependency wait while the split
+//            runs and the next layer's split is launched on time.  Measured at 32k
+//            context, one sequence: 11.4 us per layer against 13.6 us.
 constexpr int kFullConsumerWarps = 8;
-constexpr int kLiteConsumerWarps = 4;
-constexpr int kFullThreads = (kFullConsumerWarps + 2) * 32;   // 320
-constexpr int kLiteThreads = (kLiteConsumerWarps + 1) * 32;   // 160
-constexpr int kLiteCtasPerSm = 3;
-constexpr int kLiteSmemBudget = 74 * 1024;                    // per CTA, three per SM
+constexpr int kCompactConsumerWarps = 4;
+constexpr int kFullThreads = (kFullConsumerWarps + 2) * 32;         // 320
+constexpr int kCompactThreads = (kCompactConsumerWarps + 2) * 32;   // 192
 constexpr int kMaxStages = 8;
 constexpr int kBlockPos = 16;                            // positions per mma step
 constexpr float kLog2e = 1.4426950408889634f;
@@ -82,22 +84,22 @@ constexpr int kMergePad = 8;       // floats after o[D] in an exchange row: 4 un
 
 __host__ __device__ inline int vteb_round_up(int x, int m) { return (x + m - 1) / m * m; }
 
-__host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim, int lite = 0) {
+__host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim, int compact = 0) {
     FastPlan p;
     p.ok = 0;
     p.hg = p.n_hgroups = p.wph = p.active_warps = p.tile = p.row_bytes = p.row_pitch = 0;
     p.stage_bytes = p.merge_bytes = p.q_bytes = p.nstages = p.smem_bytes = 0;
-    const int cw = lite ? kLiteConsumerWarps : kFullConsumerWarps;
+    const int cw = compact ? kCompactConsumerWarps : kFullConsumerWarps;
     p.consumer_warps = cw;
-    p.loader_warps = lite ? 1 : 2;
+    p.loader_warps = 2;
     p.threads = (cw + p.loader_warps) * 32;
     if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0) return p;
     int group = num_q_heads / num_kv_heads;
     if (group > 8) return p;
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return p;
-    // full: largest divisor of num_kv_heads with hg * head_dim <= 512 halves and hg <= 8;
-    // lite: one KV head per item.
-    int cap = lite ? 1 : 512 / head_dim;
+    // largest divisor of num_kv_heads with hg * head_dim <= 512 halves and a consumer warp
+    // (two for 256-wide heads) left for every head
+    int cap = 512 / head_dim;
     if (cap > cw) cap = cw;
     int hg = 1;
     for (int d = 1; d <= cap; ++d) if (num_kv_heads % d == 0) hg = d;
@@ -111,14 +113,14 @@ __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_h
     p.active_warps = p.wph * hg * dsplit;
     p.row_bytes = hg * head_dim * 2;
     p.row_pitch = p.row_bytes + 16;
-    int tile = ((lite ? 8192 : 16384) / p.row_bytes) / kBlockPos * kBlockPos;
+    int tile = (16384 / p.row_bytes) / kBlockPos * kBlockPos;
     if (tile < kBlockPos) tile = kBlockPos;
     if (tile > 64) tile = 64;
     p.tile = tile;
     p.stage_bytes = vteb_round_up(2 * tile * p.row_pitch, 128);
     p.merge_bytes = vteb_round_up(p.active_warps * group * (head_dim + kMergePad) * 4, 128);
     p.q_bytes = hg * (head_dim / 8) * 32 * 4;   // one fragment image per KV head, shared by its warps
-    int left = (lite ? kLiteSmemBudget : kSmemBudget) - kCtrlBytes - p.merge_bytes - p.q_bytes;
+    int left = kSmemBudget - kCtrlBytes - p.merge_bytes - p.q_bytes;
     int n = left / p.stage_bytes;
     if (n > kMaxStages) n = kMaxStages;
     if (n < 2) return p;

@@ -131,7 +131,7 @@ int check_nccl(int r, const char* what) {
 
 // Per-process record of which in-library kernels already had their dynamic
 // shared memory limit raised.
-bool g_fast_attr_set[5] = {false, false, false, false, false};
+bool g_fast_attr_set[6] = {false, false, false, false, false, false};
 
 template <typename... Args>
 int launch_rt(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -526,9 +526,9 @@ int vteb_ipc_close_handle(void* dev_ptr) {
 }
 
 // ---- split-KV decode attention ---------------------------------------------
-static int fill_plan(int num_q_heads, int num_kv_heads, int head_dim, int lite, vteb_fast_plan* plan) {
+static int fill_plan(int num_q_heads, int num_kv_heads, int head_dim, int compact, vteb_fast_plan* plan) {
     if (!plan) return fail(VTEB_ERR_INVALID_ARGUMENT, "null plan");
-    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, lite);
+    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, compact);
     memset(plan, 0, sizeof(*plan));
     plan->ok = p.ok;
     plan->hg = p.hg;
@@ -546,10 +546,8 @@ int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fas
     return fill_plan(num_q_heads, num_kv_heads, head_dim, 0, plan);
 }
 
-int vteb_split_kv_plan_lite(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan) {
-    int rc = fill_plan(num_q_heads, num_kv_heads, head_dim, 1, plan);
-    if (rc == 0 && head_dim == 256) plan->ok = 0;   // no lite kernel is built for 256-wide heads
-    return rc;
+int vteb_split_kv_plan_compact(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan) {
+    return fill_plan(num_q_heads, num_kv_heads, head_dim, 1, plan);
 }
 
 int vteb_combine_rows_epl(int rows, int head_dim) {
@@ -614,8 +612,12 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                          (const float*)partial_o, (__half*)output, num_q_heads, head_dim, max_chunks);
     }
 
-    const bool lite = (flags & VTEB_ATTN_LITE) != 0 && head_dim != 256;
-    const vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, lite ? 1 : 0);
+    bool compact = (flags & VTEB_ATTN_COMPACT) != 0;
+    vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, compact ? 1 : 0);
+    if (compact && !p.ok) {   // more KV heads per group than four consumer warps can serve
+        compact = false;
+        p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, 0);
+    }
     if (!p.ok)
         return fail(VTEB_ERR_UNSUPPORTED, "fast split kernel does not cover Hq=%d Hkv=%d D=%d; pass VTEB_ATTN_COMPAT",
                     num_q_heads, num_kv_heads, head_dim);
@@ -624,7 +626,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     if (n_ctas <= 0) {
         int sms = 0;
         if ((rc = check_rt(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g_device), "sm count"))) return rc;
-        n_ctas = lite ? sms * vteb::kLiteCtasPerSm : sms;
+        n_ctas = sms;
     }
     if (n_ctas > items) n_ctas = (int)items;
 
@@ -632,8 +634,9 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                                int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*, const __half*, void*, int);
     FastKernel fk;
     int slot;
-    if (lite && head_dim == 64) { fk = vteb_split_kv_partial_lite_d64_kernel; slot = 3; }
-    else if (lite) { fk = vteb_split_kv_partial_lite_d128_kernel; slot = 4; }
+    if (compact && head_dim == 64) { fk = vteb_split_kv_partial_compact_d64_kernel; slot = 3; }
+    else if (compact && head_dim == 128) { fk = vteb_split_kv_partial_compact_d128_kernel; slot = 4; }
+    else if (compact) { fk = vteb_split_kv_partial_compact_d256_kernel; slot = 5; }
     else if (head_dim == 64) { fk = vteb_split_kv_partial_d64_kernel; slot = 0; }
     else if (head_dim == 128) { fk = vteb_split_kv_partial_d128_kernel; slot = 1; }
     else { fk = vteb_split_kv_partial_d256_kernel; slot = 2; }
