@@ -135,6 +135,11 @@ __device__ __forceinline__ void copy_rows_async(const unsigned char* src, const 
 // layer's launch.  HBM then stays busy while this launch drains its tail and the
 // combine runs, and the next launch starts from L2.  Every byte is still read
 // from HBM once per step.  Requests are 8 KB each, spread over the lanes.
+// The prefetch only pays while a whole layer's K and V stay in L2 until the next launch reads
+// them: above this many bytes per tensor (the grid's total) it is skipped.  Measured at one
+// million positions (0.5 GB per tensor): prefetching cost 15 % of the throughput.
+constexpr long long kL2PrefetchMaxBytes = 24ll << 20;
+
 __device__ __forceinline__ void prefetch_range_l2(const unsigned char* base, long long bytes, int lane) {
     constexpr long long kPiece = 8192;
     for (long long off = (long long)lane * kPiece; off < bytes; off += 32 * kPiece) {
@@ -300,7 +305,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
         if (a.next_k_cache != nullptr && plan.n_hgroups == 1 && total_items <= (int)gridDim.x && (int)blockIdx.x < total_items) {
             const ItemGeometry g = first_geom;
-            if (g.end > g.start)
+            if (g.end > g.start && (long long)(g.end - g.start) * pos_stride * total_items <= kL2PrefetchMaxBytes)
                 prefetch_range_l2(reinterpret_cast<const unsigned char*>(a.next_k_cache) +
                                       2ll * (long long)g.b * a.kv_batch_stride + (long long)g.start * pos_stride,
                                   (long long)(g.end - g.start) * pos_stride, lane);
@@ -341,7 +346,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
         if (a.next_v_cache != nullptr && plan.n_hgroups == 1 && total_items <= (int)gridDim.x && (int)blockIdx.x < total_items) {
             const ItemGeometry g = first_geom;
-            if (g.end > g.start)
+            if (g.end > g.start && (long long)(g.end - g.start) * pos_stride * total_items <= kL2PrefetchMaxBytes)
                 prefetch_range_l2(reinterpret_cast<const unsigned char*>(a.next_v_cache) +
                                       2ll * (long long)g.b * a.kv_batch_stride + (long long)g.start * pos_stride,
                                   (long long)(g.end - g.start) * pos_stride, lane);
