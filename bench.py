@@ -39,8 +39,10 @@ METRIC = "decode_attention_achieved_hbm_bandwidth"
 UNIT = "TB/s"
 NOMINAL_PEAK_TBS = 8.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the split kernel, from the ncu
-# capture summarised in profiles/split_kv_partial_d128_c2_32k_ncu.md (same launch size).
-NCU_TRAFFIC_BYTES = {"c2": 33603328}
+# captures summarised in profiles/split_kv_partial_compact_d128_c2_32k_ncu.md (compact CTA shape,
+# the default for this workload) and profiles/split_kv_partial_d128_c2_32k_ncu.md (full shape);
+# same launch size as the bench's.
+NCU_TRAFFIC_BYTES = {("c2", True): 33612117, ("c2", False): 33603328}
 
 
 def measured_peaks():
@@ -337,7 +339,7 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": ex.kernel_launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                          "frac": achieved / peak_gbs, "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if not (args.compat or args.layers) else None,
+                         "traffic": NCU_TRAFFIC_BYTES.get((args.workload, ex.dispatcher.compact)) if not (args.compat or args.layers) else None,
                          "kernel": kern["split_name"], "kernel_us": kern["split_us"],
                          "combine_us": kern["combine_us"], "algorithmic_bytes_per_launch": int(split_bytes)},
             "clocks": clocks, "parity": parity,
