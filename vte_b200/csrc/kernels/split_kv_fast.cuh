@@ -10,7 +10,7 @@
 // Loader warp K (the first warp after the consumers): for every tile of `tile` positions it waits for a free
 // stage, writes the tile header, and copies the K rows (row_bytes contiguous
 // bytes covering the group's heads) with 16-byte asynchronous copies, one
-// 512-byte piece per warp instruction, into rows padded by 16 bytes.  Loader
+// 512-byte piece per warp instruction, into the 128-byte-swizzled tile layout.  Loader
 // warp V (warp 9) follows the headers and copies the V rows.  The copies'
 // completion is counted on the stage's "full" mbarrier.  Rows past the end of
 // the item are filled from the item's last row so that every row a consumer
@@ -77,8 +77,14 @@ __device__ __forceinline__ void raise_abort(volatile int* abort_word, int* statu
     }
 }
 
+// Shared-memory layout of a K (or V) tile: column blocks of 128 bytes (64 halves).  Block cb
+// starts at cb * blk_bytes (blk_bytes = tile * 128); inside it position row r is at r * 128 and
+// its 16-byte chunk c sits at ((c ^ (r & 7)) << 4).  This is the 128-byte swizzle a tensor-map
+// copy with a 128-byte-wide box produces, and it keeps the eight row addresses of an ldmatrix
+// on distinct banks without padding.  Tiles start on 1024-byte shared addresses.
+//
 // Copies `nrows` (a multiple of 16) position rows of `row_bytes` <= 1024 bytes each from
-// global to padded shared rows with 16-byte asynchronous copies; rows at or past `nvalid`
+// global into that layout with 16-byte asynchronous copies; rows at or past `nvalid`
 // are taken from `src_last` (the item's last row).  A warp instruction moves 512 bytes:
 // one piece of a long row, or several whole short rows (256-byte rows: two per
 // instruction).  Eight instructions' addresses are formed first and their copies issued
@@ -87,31 +93,34 @@ __device__ __forceinline__ void raise_abort(volatile int* abort_word, int* statu
 // latency on every row (measured: ~230 cycles per row instead of ~16).
 __device__ __forceinline__ void copy_rows_async(const unsigned char* src, const unsigned char* src_last,
                                                 uint32_t dst, int nrows, int nvalid, int row_bytes,
-                                                int row_pitch, long long pos_stride, int lane) {
+                                                int blk_bytes, long long pos_stride, int lane) {
     if (row_bytes >= 512) {
         const bool piece0 = lane * 16 < row_bytes;                    // bytes [0, 512) of the row
         const bool piece1 = 512 + lane * 16 < row_bytes;              // bytes [512, 1024)
-        src += lane * 16; src_last += lane * 16; dst += lane * 16;
-        for (int r0 = 0; r0 < nrows; r0 += 8) {
+        src += lane * 16; src_last += lane * 16;
+        dst += (lane >> 3) * blk_bytes;                               // this lane's column block
+        const uint32_t chunk = (lane & 7) << 4;
+        for (int r0 = 0; r0 < nrows; r0 += 8) {                       // r0 & 7 == 0: row i of the group has r & 7 == i
             const unsigned char* s[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) s[i] = (r0 + i < nvalid) ? src + (long long)i * pos_stride : src_last;
             if (piece0) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch, s[i]);
+                for (int i = 0; i < 8; ++i) async_copy_16(dst + i * 128 + (chunk ^ (i << 4)), s[i]);
             }
             if (piece1) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) async_copy_16(dst + i * row_pitch + 512, s[i] + 512);
+                for (int i = 0; i < 8; ++i) async_copy_16(dst + 4 * blk_bytes + i * 128 + (chunk ^ (i << 4)), s[i] + 512);
             }
             src += 8 * pos_stride;
-            dst += 8 * row_pitch;
+            dst += 8 * 128;
         }
     } else {
         const int lanes_per_row = row_bytes >> 4;                     // 16 for 256-byte rows, 8 for 128
         const int rows_per_instr = 32 / lanes_per_row;
-        const int my_row = lane / lanes_per_row, my_col = (lane - my_row * lanes_per_row) * 16;
-        src += my_col; src_last += my_col;
+        const int my_row = lane / lanes_per_row, my_chunk = lane - my_row * lanes_per_row;
+        src += my_chunk * 16; src_last += my_chunk * 16;
+        dst += (my_chunk >> 3) * blk_bytes;
         for (int r0 = 0; r0 < nrows; r0 += 8 * rows_per_instr) {
             const unsigned char* s[8];
             uint32_t d[8];
@@ -121,7 +130,7 @@ __device__ __forceinline__ void copy_rows_async(const unsigned char* src, const 
                 const int r = r0 + i * rows_per_instr + my_row;
                 on[i] = r < nrows && my_row < rows_per_instr;
                 s[i] = (r < nvalid) ? src + (long long)r * pos_stride : src_last;
-                d[i] = dst + r * row_pitch + my_col;
+                d[i] = dst + r * 128 + (((my_chunk ^ r) & 7) << 4);
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) if (on[i]) async_copy_16(d[i], s[i]);
@@ -204,7 +213,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     TileHeader* headers = reinterpret_cast<TileHeader*>(smem_raw + kHeaderOffset);
     float* merge = reinterpret_cast<float*>(smem_raw + kCtrlBytes);
     uint32_t* q_store = reinterpret_cast<uint32_t*>(smem_raw + kCtrlBytes + plan.merge_bytes);
+    // stages start on the next 1024-byte shared address (the plan reserves the slack)
     unsigned char* stages = smem_raw + kCtrlBytes + plan.merge_bytes + plan.q_bytes;
+    stages += (kStageAlign - (smem_u32(stages) & (kStageAlign - 1))) & (kStageAlign - 1);
 
     const uint32_t bar0 = smem_u32(smem_raw);
     const uint32_t full0 = bar0 + kBarFull * 1, empty0 = bar0 + kBarEmpty, hdr0 = bar0 + kBarHeader;
@@ -286,7 +297,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         (long long)pos0 * pos_stride;
                     const unsigned char* src_last = src + (long long)(g.end - 1 - pos0) * pos_stride;
                     const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes);
-                    copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
+                    copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.blk_bytes, pos_stride, lane);
                     async_copy_arrive(bar);
                 } else {
                     mbar_arrive(bar);      // no copies belong to this tile
@@ -335,8 +346,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     2ll * ((long long)hd.b * a.kv_batch_stride + (long long)hd.hgroup * plan.hg * D) +
                     (long long)hd.pos0 * pos_stride;
                 const unsigned char* src_last = src + (long long)(hd.last_pos - hd.pos0) * pos_stride;
-                const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_pitch;
-                copy_rows_async(src, src_last, dst, nrows, hd.nvalid, plan.row_bytes, plan.row_pitch, pos_stride, lane);
+                const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_bytes;
+                copy_rows_async(src, src_last, dst, nrows, hd.nvalid, plan.row_bytes, plan.blk_bytes, pos_stride, lane);
                 async_copy_arrive(bar);
             } else {
                 mbar_arrive(bar);
@@ -405,9 +416,16 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     bool first_item = true;
 
     // Lane-constant parts of the ldmatrix addresses.
-    const int k_lane_off = ((lane & 7) + ((lane >> 4) << 3)) * plan.row_pitch + (((lane >> 3) & 1) * 8 + hh * D) * 2;
-    const int v_lane_off = ((lane & 7) + (((lane >> 3) & 1) << 3)) * plan.row_pitch + ((lane >> 4) * 8 + hh * D + dhalf * DW) * 2;
-    const int v_tile_off = plan.tile * plan.row_pitch;
+    // K, per 16-half k-step: matrices (rows 0-7, chunk 0), (rows 0-7, chunk 1), (rows 8-15, chunk 0),
+    // (rows 8-15, chunk 1); V, per 16 output columns: (rows 0-7, chunk 0), (rows 8-15, chunk 0),
+    // (rows 0-7, chunk 1), (rows 8-15, chunk 1).  A lane's row has r & 7 == lane & 7, so the
+    // swizzle term of its address is a lane constant XORed with the k-step's chunk pair.
+    const int blk_bytes = plan.blk_bytes;
+    const uint32_t k_lane_off = ((lane & 7) + ((lane >> 4) << 3)) * 128 + hh * (D / 64) * blk_bytes;
+    const uint32_t k_lane_x = ((((lane >> 3) & 1) ^ (lane & 7)) << 4);
+    const uint32_t v_lane_off = ((lane & 7) + (((lane >> 3) & 1) << 3)) * 128 +
+                                (hh * (D / 64) + dhalf * (DW / 64)) * blk_bytes + plan.tile * plan.row_bytes;
+    const uint32_t v_lane_x = (((lane >> 4) ^ (lane & 7)) << 4);
 
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
     grid_dependency_wait();
@@ -442,14 +460,15 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             if (((blk0 + blk) & wph_mask) != sub) continue;
             // ---- S = Q K^T: s[0] positions 0..7, s[1] positions 8..15; two accumulation
             // chains each; K fragments are fetched eight k-steps at a time
-            const uint32_t kaddr = tile_base + r0 * plan.row_pitch + k_lane_off;
+            const uint32_t kaddr = (tile_base + r0 * 128 + k_lane_off) | k_lane_x;
             float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, s_alt[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
             constexpr int KC = KS < 8 ? KS : 8;
 #pragma unroll
             for (int kc = 0; kc < KS; kc += KC) {
                 uint32_t kf[KC][4];
 #pragma unroll
-                for (int i = 0; i < KC; ++i) ldmatrix_x4(kaddr + (kc + i) * 32, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
+                for (int i = 0; i < KC; ++i)
+                    ldmatrix_x4((kaddr ^ (((kc + i) & 3) << 5)) + ((kc + i) >> 2) * blk_bytes, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
 #pragma unroll
                 for (int i = 0; i < KC; i += 2) {
                     const int ks = kc + i;
@@ -462,12 +481,12 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 }
             }
             // ---- V fragments do not depend on the softmax: fetch the first 64 columns now
-            const uint32_t vaddr = tile_base + v_tile_off + r0 * plan.row_pitch + v_lane_off;
+            const uint32_t vaddr = (tile_base + r0 * 128 + v_lane_off) | v_lane_x;
             constexpr int VC = 4;                 // ldmatrix.x4.trans per chunk = 64 output columns
             constexpr int NVC = NT / (2 * VC);    // chunks
             uint32_t vf[2][VC][4];
 #pragma unroll
-            for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr + i * 32, vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
+            for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr ^ (i << 5), vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
             // ---- online softmax (log2 domain); positions past the item's end are masked
             const int left = nvalid - r0;         // valid positions in this block (may exceed 16)
             float mx = kNeutralM;
@@ -513,7 +532,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 if (ch + 1 < NVC) {
 #pragma unroll
                     for (int i = 0; i < VC; ++i)
-                        ldmatrix_x4_trans(vaddr + ((ch + 1) * VC + i) * 32, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
+                        ldmatrix_x4_trans((vaddr ^ (i << 5)) + (ch + 1) * blk_bytes, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
                                           vf[(ch + 1) & 1][i][2], vf[(ch + 1) & 1][i][3]);
                 }
 #pragma unroll

@@ -67,7 +67,7 @@ struct FastPlan {
     int active_warps;  // wph * hg
     int tile;          // positions per stage
     int row_bytes;     // bytes of one position's K (or V) row for the head group
-    int row_pitch;     // row_bytes + 16: keeps ldmatrix row addresses on distinct banks
+    int blk_bytes;     // one 128-byte-wide column block of a tile: tile * 128
     int stage_bytes;   // K tile + V tile
     int merge_bytes;   // per-warp (m, l, o) exchange area
     int q_bytes;       // Q operand fragments in shared memory (keeps them out of registers)
@@ -80,6 +80,7 @@ struct FastPlan {
 };
 
 constexpr int kCtrlBytes = 1024;   // barriers, abort word, tile headers
+constexpr int kStageAlign = 1024;  // stages start on a 1024-byte shared-memory address (the 128-byte swizzle repeats every 8 rows)
 constexpr int kMergePad = 8;       // floats after o[D] in an exchange row: 4 unused, m, l, 2 unused
 
 __host__ __device__ inline int vteb_round_up(int x, int m) { return (x + m - 1) / m * m; }
@@ -87,7 +88,7 @@ __host__ __device__ inline int vteb_round_up(int x, int m) { return (x + m - 1) 
 __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim, int compact = 0) {
     FastPlan p;
     p.ok = 0;
-    p.hg = p.n_hgroups = p.wph = p.active_warps = p.tile = p.row_bytes = p.row_pitch = 0;
+    p.hg = p.n_hgroups = p.wph = p.active_warps = p.tile = p.row_bytes = p.blk_bytes = 0;
     p.stage_bytes = p.merge_bytes = p.q_bytes = p.nstages = p.smem_bytes = 0;
     const int cw = compact ? kCompactConsumerWarps : kFullConsumerWarps;
     p.consumer_warps = cw;
@@ -112,20 +113,20 @@ __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_h
     if (p.wph < 1) return p;
     p.active_warps = p.wph * hg * dsplit;
     p.row_bytes = hg * head_dim * 2;
-    p.row_pitch = p.row_bytes + 16;
     int tile = (16384 / p.row_bytes) / kBlockPos * kBlockPos;
     if (tile < kBlockPos) tile = kBlockPos;
     if (tile > 64) tile = 64;
     p.tile = tile;
-    p.stage_bytes = vteb_round_up(2 * tile * p.row_pitch, 128);
+    p.blk_bytes = tile * 128;
+    p.stage_bytes = 2 * tile * p.row_bytes;
     p.merge_bytes = vteb_round_up(p.active_warps * group * (head_dim + kMergePad) * 4, 128);
     p.q_bytes = hg * (head_dim / 8) * 32 * 4;   // one fragment image per KV head, shared by its warps
-    int left = kSmemBudget - kCtrlBytes - p.merge_bytes - p.q_bytes;
+    int left = kSmemBudget - kCtrlBytes - p.merge_bytes - p.q_bytes - kStageAlign;
     int n = left / p.stage_bytes;
     if (n > kMaxStages) n = kMaxStages;
     if (n < 2) return p;
     p.nstages = n;
-    p.smem_bytes = kCtrlBytes + p.merge_bytes + p.q_bytes + n * p.stage_bytes;
+    p.smem_bytes = kCtrlBytes + p.merge_bytes + p.q_bytes + kStageAlign + n * p.stage_bytes;
     p.ok = 1;
     return p;
 }
