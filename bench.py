@@ -233,7 +233,7 @@ def run_ours(args, rank, world, local_rank):
                                  programmatic=not args.no_pdl, compat=args.compat,
                                  prefetch_next_layer=not args.no_prefetch,
                                  fused_combine=args.fuse, variant=args.variant, rope=args.rope,
-                                 rope_theta=cfg.rope_theta or 1e6)
+                                 rope_theta=cfg.rope_theta or 1e6, tensor_maps=not args.no_tma)
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
@@ -322,6 +322,7 @@ def run_ours(args, rank, world, local_rank):
             "config": config_json(cfg, args.workload, lengths, n_layers, n_kv, ex.dispatcher.max_chunks, world,
                                   {"input_generation": "host, seeded" if host_gen else "device fill (counter-based normal)",
                                    "programmatic_dependent_launch": not args.no_pdl,
+                                   "kv_tile_copies": "tensor-map (TMA) boxes for whole tiles, 16-byte cp.async for ragged ends" if ex.dispatcher.tensor_maps else "16-byte cp.async",
                                    "next_layer_l2_prefetch": not args.no_prefetch and cfg.batch == 1,
                                    "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, compact CTAs" if ex.dispatcher.compact else "fast, full CTAs"),
                                    "step_contents": {"off": "split + combine per layer",
@@ -509,6 +510,7 @@ def main():
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")
+    ap.add_argument("--no-tma", action="store_true", help="fetch every K/V tile with 16-byte asynchronous copies (no tensor-map copies)")
     ap.add_argument("--rope", default="off", choices=["off", "separate", "fused"],
                     help="also run the rotary embedding and the cache append inside the step: as the standalone "
                          "rotation launch, or folded into the append (K) and the split kernel's Q load")

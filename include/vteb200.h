@@ -155,6 +155,14 @@ int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fas
  * shortens a layer whose whole split launch lasts only some microseconds.  `ok` is 0 when
  * a head group needs more than four consumer warps. */
 int vteb_split_kv_plan_compact(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
+/* Encodes the 128-byte tensor map the fast split kernels take for a K or V cache: the cache
+ * seen as `n_rows` position rows (all sequences, one after another) of `row_halves` =
+ * Hkv * D fp16 values, in boxes of 64 values x `box_rows` rows (the plan's `tile`) with the
+ * 128-byte swizzle.  `cache` must be 16-byte aligned, `row_halves` a multiple of 64.  The
+ * kernels use it for whole tiles; ragged ends still travel as 16-byte copies.  No reference
+ * counterpart: the reference's kernels read the cache with scalar loads
+ * (flash_attention_split_kv_partial.hip.template:86-93). */
+int vteb_kv_tensor_map(void* out_128_bytes, const void* cache, long long n_rows, int row_halves, int box_rows);
 /* Columns per lane of the short-list combine kernel (split counts up to 64): a warp
  * merges 32 * epl columns of one (sequence, head) row. */
 int vteb_combine_rows_epl(int rows, int head_dim);
@@ -178,6 +186,7 @@ int vteb_combine_rows_epl(int rows, int head_dim);
 #define VTEB_ATTN_WRITE_EMPTY_O 2
 #define VTEB_ATTN_PROGRAMMATIC 4
 #define VTEB_ATTN_COMPACT 16   /* compact CTA shape where it applies, see vteb_split_kv_plan_compact */
+#define VTEB_ATTN_NO_TENSOR_MAPS 32   /* fetch every tile with 16-byte asynchronous copies (no tensor-map copies) */
 int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache,
                          const int* kv_offsets, void* output, int out_is_f32,
                          float* partial_m, float* partial_l, float* partial_o, int* work,

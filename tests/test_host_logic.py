@@ -165,7 +165,8 @@ def test_fused_launch_list_is_append_plus_one_launch():
     assert len(launches) == 2
     fp, ap, gp, bp, sp = launches[1]
     assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_d128_kernel"])
-    assert ap[-1].value == 2 and ap[-2].value == mapping()['blk.0.attention.output']
+    assert ap[22].value == 2 and ap[21].value == mapping()['blk.0.attention.output']
+    assert all(isinstance(a, ctypes.Structure) and ctypes.sizeof(a) == 128 for a in ap[23:25])   # the two tensor maps
     # three KV heads per group cannot use all eight consumer warps: no in-launch combine
     d2, *_ = make_dispatcher({'attention.head_count': 12, 'attention.head_count_kv': 3, 'attention.key_length': 128},
                              fused_combine=True)
@@ -185,7 +186,7 @@ def test_fused_rope_launch_list_and_standalone_rotation_launch():
     assert symbols[:2] == ["kv_cache_append_rope_kernel", "vteb_split_kv_partial_rope_d256_kernel"]
     (fa, aa, ga, ba, sa), (fp, ap, gp, bp, sp) = launches[:2]
     assert len(aa) == len(KERNEL_SIGNATURES["kv_cache_append_rope_kernel"]) == 12
-    assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_rope_d256_kernel"]) == 27
+    assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_rope_d256_kernel"]) == 29
     for args in (aa, ap):
         assert [a.value for a in args[-4:]] == [0x7300_0000_0000, 0x7300_1000_0000, 2, 64]
     assert ga == (4, 2, 1) and ba == (256, 1, 1)
@@ -200,7 +201,7 @@ def test_fused_rope_launch_list_and_standalone_rotation_launch():
         make_dispatcher(meta128, fuse_rope=True, compat=True)
     dc, rtc, *_ = make_dispatcher(meta128, fuse_rope=True, context_length=4096)           # one sequence: compact shape
     m128 = dict(mapping(), rope_cos=0x7300_0000_0000, rope_sin=0x7300_1000_0000)
-    assert dc.compact and len(dc.build_launches(0, m128, 0x7200_0000_0000)[1][1]) == 27
+    assert dc.compact and len(dc.build_launches(0, m128, 0x7200_0000_0000)[1][1]) == 29
     assert rtc.loaded[1][1] == "vteb_split_kv_partial_compact_rope_d128_kernel"
     with pytest.raises(CudaSafetyError):
         make_dispatcher(dict(meta, rotary_dim=48), fuse_rope=True)

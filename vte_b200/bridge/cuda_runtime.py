@@ -47,6 +47,7 @@ ATTN_COMPAT = 1
 ATTN_WRITE_EMPTY_O = 2
 ATTN_PROGRAMMATIC = 4
 ATTN_COMPACT = 16
+ATTN_NO_TENSOR_MAPS = 32
 
 ERR_DEVICE_STATUS = -6
 
@@ -57,6 +58,11 @@ class FastPlan(ctypes.Structure):
                 ("tile", ctypes.c_int), ("nstages", ctypes.c_int), ("smem_bytes", ctypes.c_int),
                 ("threads", ctypes.c_int), ("combine_dsplit", ctypes.c_int),
                 ("combine_smem_bytes", ctypes.c_int)]
+
+
+class KvTensorMap(ctypes.Structure):
+    """The 128-byte tensor map of a K or V cache, passed to the fast split kernels by value."""
+    _fields_ = [("opaque", ctypes.c_uint64 * 16)]
 
 
 def default_library_path() -> Path:
@@ -121,6 +127,7 @@ def _declare(lib):
         "vteb_ipc_close_handle": (i, [vp]),
         "vteb_split_kv_plan": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
         "vteb_split_kv_plan_compact": (i, [i, i, i, ctypes.POINTER(FastPlan)]),
+        "vteb_kv_tensor_map": (i, [vp, vp, ctypes.c_longlong, i, i]),
         "vteb_combine_rows_epl": (i, [i, i]),
         "vteb_split_kv_decode": (i, [vp, vp, vp, vp, vp, i, vp, vp, vp, vp, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_split_kv_decode_noalloc": (i, [vp, vp, vp, vp, vp, i, i, i, i, i, f, ll, i, i, u, i, vp]),
@@ -644,6 +651,14 @@ class CudaRuntime:
         fn = self._lib.vteb_split_kv_plan_compact if compact else self._lib.vteb_split_kv_plan
         self._check_error(fn(num_q_heads, num_kv_heads, head_dim, ctypes.byref(plan)), "vteb_split_kv_plan")
         return plan
+
+    def kv_tensor_map(self, cache_ptr: int, n_rows: int, row_halves: int, box_rows: int) -> KvTensorMap:
+        """Tensor map over a cache of `n_rows` position rows of `row_halves` fp16 values (boxes of
+        64 values x `box_rows` rows, 128-byte swizzle) for the fast split kernels."""
+        tm = KvTensorMap()
+        self._check_error(self._lib.vteb_kv_tensor_map(ctypes.byref(tm), ctypes.c_void_p(int(cache_ptr)), int(n_rows),
+                                                       int(row_halves), int(box_rows)), "vteb_kv_tensor_map")
+        return tm
 
     def combine_rows_epl(self, rows: int, head_dim: int) -> int:
         return int(self._lib.vteb_combine_rows_epl(int(rows), int(head_dim)))

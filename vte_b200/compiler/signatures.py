@@ -15,8 +15,9 @@ import ctypes
 P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 _REFERENCE_PARTIAL = [P, P, P, P, P, P, I, I, I, F, P, I, I]
-_FAST_PARTIAL = _REFERENCE_PARTIAL + [I, I, I, P, P, P, P, P, P, I]
-# ... batch, min_chunk, flags, seq_order, ticket, status, next K, next V, output, out_kind
+_FAST_PARTIAL = _REFERENCE_PARTIAL + [I, I, I, P, P, P, P, P, P, I, ctypes.Structure, ctypes.Structure]
+# ... batch, min_chunk, flags, seq_order, ticket, status, next K, next V, output, out_kind,
+#     tensor map of the K cache, tensor map of the V cache (128 bytes each, by value)
 _ROPE_TAIL = [P, P, I, I]                                 # cos table, sin table, rope_type, rotary_dim
 _REDUCE = [P, P, P, P, I, I, I]
 _FAST_COMBINE = _REDUCE + [I, P]                          # dsplit, ticket

@@ -33,7 +33,7 @@ class DecodeAttentionExecutor:
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
                  emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
                  fused_combine: Optional[bool] = None, variant: str = "auto", rope: str = "off",
-                 rope_theta: float = 1e6):
+                 rope_theta: float = 1e6, tensor_maps: bool = True):
         self.hip = hip
         # rope: "off" = Q and K arrive rotated; "separate" = the reference's standalone rotation
         # launch runs before the append (rotating the projections in place); "fused" = the append
@@ -84,7 +84,7 @@ class DecodeAttentionExecutor:
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
             prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant,
-            fuse_rope=(rope == "fused"))
+            fuse_rope=(rope == "fused"), tensor_maps=tensor_maps)
 
         A = allocator.allocate
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]

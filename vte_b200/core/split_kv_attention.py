@@ -32,6 +32,7 @@ MAX_SPLITS = 256
 TARGET_CHUNK_POSITIONS = 256      # smallest chunk length aimed at when many sequences share the GPU
 FLAG_WRITE_EMPTY_O = 1
 FLAG_DIRECT_OUTPUT = 2
+FLAG_TENSOR_MAPS = 4
 COMPACT_MAX_CONTEXT = 262144      # one sequence up to this long: the compact CTA shape (launches of tens of microseconds)
 UNSPLIT_MAX_CONTEXT = 128         # below this, one CTA per (sequence, head group) finishes before a combine could launch
 
@@ -82,7 +83,8 @@ class SplitKVAttentionDispatcher:
                  batch_size: int = 1, *, num_splits: int | None = None, fixed_chunk_size=None,
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
                  strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True,
-                 fused_combine: bool | None = None, variant: str = "auto", fuse_rope: bool = False):
+                 fused_combine: bool | None = None, variant: str = "auto", fuse_rope: bool = False,
+                 tensor_maps: bool = True):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -177,6 +179,11 @@ class SplitKVAttentionDispatcher:
                 raise CudaSafetyError(f"rope_type {self.rope_type} not in 0, 1, 2")
             if self.rope_type == 2 and (self.rotary_dim not in (32, 64, 128, 256) or self.rotary_dim > self.head_dim):
                 raise CudaSafetyError(f"rotary_dim {self.rotary_dim} must be 32, 64, 128 or 256 and at most head_dim")
+
+        # tensor_maps: whole K/V tiles are fetched with tensor-map (TMA) box copies; ragged ends and
+        # caches whose sequence stride is not a whole number of position rows use 16-byte copies
+        self.tensor_maps = bool(tensor_maps) and hip is not None and hasattr(hip, 'kv_tensor_map')
+        self._tensor_map_cache = {}
 
         self._kernel_cache = {}
         self._rows_combine = False
@@ -283,6 +290,25 @@ class SplitKVAttentionDispatcher:
     def partial_buffers(self):
         return self._partial_m, self._partial_l, self._partial_o
 
+    # -- tensor maps ----------------------------------------------------------------
+    @staticmethod
+    def _null_tensor_map():
+        from ..bridge.cuda_runtime import KvTensorMap
+        return KvTensorMap()
+
+    def _tensor_maps_for(self, k_cache_ptr: int, v_cache_ptr: int, kv_batch_stride: int, batch: int):
+        """(K map, V map) for one layer's caches, or (None, None) when tensor-map copies do not apply."""
+        row_halves = self.num_kv_heads * self.head_dim
+        if not self.tensor_maps or row_halves % 64 or kv_batch_stride % row_halves:
+            return None, None
+        rows_per_seq = kv_batch_stride // row_halves if kv_batch_stride else self.context_length
+        n_rows = max(1, rows_per_seq * max(1, batch))
+        key = (k_cache_ptr, v_cache_ptr, n_rows)
+        if key not in self._tensor_map_cache:
+            self._tensor_map_cache[key] = (self.hip.kv_tensor_map(k_cache_ptr, n_rows, row_halves, self._plan.tile),
+                                           self.hip.kv_tensor_map(v_cache_ptr, n_rows, row_halves, self._plan.tile))
+        return self._tensor_map_cache[key]
+
     # -- launches -----------------------------------------------------------------
     def _validate(self, batch, q_ptr, k_cache_ptr, v_cache_ptr, output_ptr, kv_offset_ptr, kv_batch_stride):
         if batch <= 0 or batch > self.batch_size:
@@ -367,10 +393,15 @@ class SplitKVAttentionDispatcher:
         if direct:
             flags |= FLAG_DIRECT_OUTPUT
         pass_output = self.fused_combine or direct
+        tmap_k, tmap_v = self._tensor_maps_for(k_cache_ptr, v_cache_ptr, kv_batch_stride, batch)
+        if tmap_k is not None:
+            flags |= FLAG_TENSOR_MAPS
+        else:
+            tmap_k, tmap_v = self._null_tensor_map(), self._null_tensor_map()
         partial_args = reference_partial_args + [
             ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4),
             vp(next_k), vp(next_v),
-            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0)] + rope_tail
+            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0), tmap_k, tmap_v] + rope_tail
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
         if self.fused_combine or direct:
             return [append, partial]

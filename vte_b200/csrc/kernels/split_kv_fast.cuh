@@ -40,10 +40,14 @@ struct FastArgs {
     void* output; int out_kind;   // out_kind != 0: combine inside this launch (1 fp16, 2 fp32, 3 shard state)
     // rotary tables for the kernels that rotate Q while loading it (null otherwise)
     const __half* rope_cos; const __half* rope_sin; int rope_type, rotary_dim;
+    // tensor maps over the K and V caches (rows = positions of all sequences, 64-half boxes of
+    // `tile` rows, 128-byte swizzle); used for whole tiles when kFlagTensorMaps is set
+    const KvTensorMap* tmap_k; const KvTensorMap* tmap_v;
 };
 
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
 constexpr int kFlagDirectOutput = 2;  // max_chunks == 1: normalise and store the attention output here, no partials
+constexpr int kFlagTensorMaps = 4;    // tmap_k / tmap_v are valid: whole tiles are fetched with tensor-map copies
 
 // Stores four (or two) normalised output values; out_kind 1 = fp16, 2 = fp32.
 __device__ __forceinline__ void store_out4(void* output, int out_kind, long long idx, float4 v) {
@@ -247,6 +251,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     grid_launch_dependents();
 
     const long long pos_stride = 2ll * a.num_kv_heads * D;      // bytes between positions
+    const bool use_tensor_maps = (a.flags & kFlagTensorMaps) != 0;
+    const int rows_per_seq = (int)(a.kv_batch_stride / (a.num_kv_heads * D));   // tensor-map rows per sequence
+    const int n_col_blocks = plan.row_bytes >> 7;
 
     // ===================================================================== K loader
     if (warp == kLoaderWarpK) {
@@ -297,8 +304,20 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         (long long)pos0 * pos_stride;
                     const unsigned char* src_last = src + (long long)(g.end - 1 - pos0) * pos_stride;
                     const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes);
-                    copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.blk_bytes, pos_stride, lane);
-                    async_copy_arrive(bar);
+                    if (use_tensor_maps && nvalid == plan.tile) {
+                        // a whole tile: one elected lane issues one box per 128-byte column block
+                        if (lane == 0) {
+                            mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
+                            const int x0 = g.hgroup * plan.hg * D, y = g.b * rows_per_seq + pos0;
+                            for (int cb = 0; cb < n_col_blocks; ++cb)
+                                tma_load_box_2d(dst + cb * plan.blk_bytes, a.tmap_k, x0 + cb * 64, y, bar);
+                        } else {
+                            mbar_arrive(bar);
+                        }
+                    } else {
+                        copy_rows_async(src, src_last, dst, nrows, nvalid, plan.row_bytes, plan.blk_bytes, pos_stride, lane);
+                        async_copy_arrive(bar);
+                    }
                 } else {
                     mbar_arrive(bar);      // no copies belong to this tile
                 }
@@ -347,8 +366,19 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     (long long)hd.pos0 * pos_stride;
                 const unsigned char* src_last = src + (long long)(hd.last_pos - hd.pos0) * pos_stride;
                 const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_bytes;
-                copy_rows_async(src, src_last, dst, nrows, hd.nvalid, plan.row_bytes, plan.blk_bytes, pos_stride, lane);
-                async_copy_arrive(bar);
+                if (use_tensor_maps && hd.nvalid == plan.tile) {
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
+                        const int x0 = hd.hgroup * plan.hg * D, y = hd.b * rows_per_seq + hd.pos0;
+                        for (int cb = 0; cb < n_col_blocks; ++cb)
+                            tma_load_box_2d(dst + cb * plan.blk_bytes, a.tmap_v, x0 + cb * 64, y, bar);
+                    } else {
+                        mbar_arrive(bar);
+                    }
+                } else {
+                    copy_rows_async(src, src_last, dst, nrows, hd.nvalid, plan.row_bytes, plan.blk_bytes, pos_stride, lane);
+                    async_copy_arrive(bar);
+                }
             } else {
                 mbar_arrive(bar);
             }
@@ -726,7 +756,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
         const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status,        \
         const __half* __restrict__ next_k_cache, const __half* __restrict__ next_v_cache,             \
-        void* __restrict__ output, int out_kind)                                                      \
+        void* __restrict__ output, int out_kind, const __grid_constant__ KvTensorMap tmap_k,          \
+        const __grid_constant__ KvTensorMap tmap_v)                                                   \
     {                                                                                                 \
         FastArgs a;                                                                                   \
         a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
@@ -738,6 +769,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
         a.output = output; a.out_kind = out_kind;                                                     \
         a.rope_cos = nullptr; a.rope_sin = nullptr; a.rope_type = 0; a.rotary_dim = 0;                \
+        a.tmap_k = &tmap_k; a.tmap_v = &tmap_v;                                                       \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM, CWARPS>(a);                                                            \
     }
@@ -754,7 +786,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         int kv_batch_stride, int max_chunks, int batch, int min_chunk, int flags,                     \
         const int* __restrict__ seq_order, int* __restrict__ ticket, int* __restrict__ status,        \
         const __half* __restrict__ next_k_cache, const __half* __restrict__ next_v_cache,             \
-        void* __restrict__ output, int out_kind,                                                      \
+        void* __restrict__ output, int out_kind, const __grid_constant__ KvTensorMap tmap_k,          \
+        const __grid_constant__ KvTensorMap tmap_v,                                                   \
         const __half* __restrict__ cos_cache, const __half* __restrict__ sin_cache,                   \
         int rope_type, int rotary_dim)                                                                \
     {                                                                                                 \
@@ -769,6 +802,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.output = output; a.out_kind = out_kind;                                                     \
         a.rope_cos = cos_cache; a.rope_sin = sin_cache; a.rope_type = rope_type;                      \
         a.rotary_dim = rotary_dim;                                                                    \
+        a.tmap_k = &tmap_k; a.tmap_v = &tmap_v;                                                       \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM, CWARPS, true>(a);                                                      \
     }

@@ -199,6 +199,28 @@ __device__ __forceinline__ void async_copy_16(uint32_t dst_smem, const void* src
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 
+// ---- tensor-map (TMA) tile copies -------------------------------------------
+// A 128-byte tensor map as the driver encodes it (CUtensorMap); kernels take it as a
+// `__grid_constant__` parameter and hand its address to the copy instruction.
+struct alignas(64) KvTensorMap { unsigned long long opaque[16]; };
+
+// Counts the calling thread's arrival on `bar` and announces `bytes` of asynchronous
+// writes that will complete on it.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// One box of a 2-D tiled tensor map (x = element index inside a row, a multiple of 8 halves;
+// y = row) from global to shared memory; the bytes complete on `bar`.  With a 64-half-wide
+// box and the map's 128-byte swizzle the box lands in the tile layout described in
+// split_kv_fast.cuh.  This CTA's own shared memory only: no cluster, no multi-CTA delivery.
+__device__ __forceinline__ void tma_load_box_2d(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst_smem), "l"(tensor_map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
 // Makes the calling thread's earlier async_copy_16 operations count as one
 // arrival on the barrier once they have all landed.
 __device__ __forceinline__ void async_copy_arrive(uint32_t bar) {

@@ -44,6 +44,9 @@ struct DriverApi {
                              unsigned, CUstream, void**, void**) = nullptr;
     CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
     CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
     bool ready = false;
 } g_drv;
 
@@ -70,6 +73,7 @@ int driver_api() {
     if ((rc = resolve("cuLaunchKernel", &g_drv.LaunchKernel))) return rc;
     if ((rc = resolve("cuLaunchKernelEx", &g_drv.LaunchKernelEx))) return rc;
     if ((rc = resolve("cuGetErrorString", &g_drv.GetErrorString))) return rc;
+    if ((rc = resolve("cuTensorMapEncodeTiled", &g_drv.TensorMapEncodeTiled))) return rc;
     g_drv.ready = true;
     return 0;
 }
@@ -132,6 +136,28 @@ int check_nccl(int r, const char* what) {
 // Per-process record of which in-library kernels already had their dynamic
 // shared memory limit raised.
 bool g_fast_attr_set[6] = {false, false, false, false, false, false};
+
+// Tensor map over a K or V cache seen as a matrix of `n_rows` position rows of `row_halves`
+// fp16 values: boxes of 64 halves x `box_rows` rows, 128-byte swizzle.
+int encode_kv_tensor_map(vteb::KvTensorMap* out, const void* cache, unsigned long long n_rows, int row_halves,
+                         int box_rows) {
+    static_assert(sizeof(vteb::KvTensorMap) == sizeof(CUtensorMap), "tensor map size");
+    int rc = driver_api();
+    if (rc) return rc;
+    if (!out || !cache || ((uintptr_t)cache & 15) || n_rows == 0 || n_rows > 0xffffffffULL || row_halves < 64 ||
+        row_halves % 64 || box_rows < 1 || box_rows > 256)
+        return fail(VTEB_ERR_INVALID_ARGUMENT, "tensor map: cache %p rows %llu row_halves %d box_rows %d", cache,
+                    n_rows, row_halves, box_rows);
+    const cuuint64_t dims[2] = {(cuuint64_t)row_halves, (cuuint64_t)n_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_halves * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem_strides[2] = {1u, 1u};
+    return check_drv(g_drv.TensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                                                const_cast<void*>(cache), dims, strides, box, elem_strides,
+                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                     "cuTensorMapEncodeTiled");
+}
 
 template <typename... Args>
 int launch_rt(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -550,6 +576,16 @@ int vteb_split_kv_plan_compact(int num_q_heads, int num_kv_heads, int head_dim, 
     return fill_plan(num_q_heads, num_kv_heads, head_dim, 1, plan);
 }
 
+int vteb_kv_tensor_map(void* out_128_bytes, const void* cache, long long n_rows, int row_halves, int box_rows) {
+    REQUIRE_INIT();
+    if (n_rows <= 0) return fail(VTEB_ERR_INVALID_ARGUMENT, "tensor map: %lld rows", n_rows);
+    vteb::KvTensorMap tm;
+    int rc = encode_kv_tensor_map(&tm, cache, (unsigned long long)n_rows, row_halves, box_rows);
+    if (rc) return rc;
+    memcpy(out_128_bytes, &tm, sizeof(tm));
+    return 0;
+}
+
 int vteb_combine_rows_epl(int rows, int head_dim) {
     int epl = head_dim / 32;
     if (epl > 8) epl = 8;
@@ -631,7 +667,8 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     if (n_ctas > items) n_ctas = (int)items;
 
     typedef void (*FastKernel)(const __half*, const __half*, const __half*, float*, float*, float*, int, int,
-                               int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*, const __half*, void*, int);
+                               int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*,
+                               const __half*, void*, int, const vteb::KvTensorMap, const vteb::KvTensorMap);
     FastKernel fk;
     int slot;
     if (compact && head_dim == 64) { fk = vteb_split_kv_partial_compact_d64_kernel; slot = 3; }
@@ -645,11 +682,25 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                            "cudaFuncSetAttribute(max dynamic shared memory)"))) return rc;
         g_fast_attr_set[slot] = true;
     }
-    const int kflags = (flags & VTEB_ATTN_WRITE_EMPTY_O) ? kFlagWriteEmptyO : 0;
+    int kflags = (flags & VTEB_ATTN_WRITE_EMPTY_O) ? kFlagWriteEmptyO : 0;
+    // Whole tiles travel as tensor-map boxes when the caches are one matrix of position rows
+    // (the stride between sequences is a whole number of rows).
+    vteb::KvTensorMap tmk, tmv;
+    memset(&tmk, 0, sizeof(tmk));
+    memset(&tmv, 0, sizeof(tmv));
+    const int row_halves = num_kv_heads * head_dim;
+    if (!(flags & VTEB_ATTN_NO_TENSOR_MAPS) && kv_batch_stride % row_halves == 0 && row_halves % 64 == 0) {
+        const unsigned long long rows_per_seq = (unsigned long long)(kv_batch_stride / row_halves);
+        const unsigned long long n_rows = batch > 1 ? rows_per_seq * batch : 0xffffffffULL;   // one sequence: its length is not known here
+        if ((rc = encode_kv_tensor_map(&tmk, k_cache, n_rows, row_halves, p.tile))) return rc;
+        if ((rc = encode_kv_tensor_map(&tmv, v_cache, n_rows, row_halves, p.tile))) return rc;
+        kflags |= kFlagTensorMaps;
+    }
     rc = launch_rt(fk, dim3(n_ctas), dim3(p.threads), (size_t)p.smem_bytes, s, pdl, qh, kh, vh,
                    partial_m, partial_l, partial_o, num_q_heads, num_kv_heads, head_dim, scale, kv_offsets,
                    (int)kv_batch_stride, max_chunks, batch, min_chunk, kflags, (const int*)nullptr, work,
-                   work + 1, (const __half*)nullptr, (const __half*)nullptr, (void*)nullptr, 0);
+                   work + 1, (const __half*)nullptr, (const __half*)nullptr, (void*)nullptr, 0,
+                   (const vteb::KvTensorMap)tmk, (const vteb::KvTensorMap)tmv);
     if (rc) return rc;
 
     if (max_chunks <= 64) {
