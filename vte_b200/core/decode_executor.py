@@ -122,6 +122,7 @@ class DecodeAttentionExecutor:
         self._stage_q = hip.host_alloc(self.L * self.q_bytes)
         self._stage_out = hip.host_alloc(self.L * self.out_bytes)
         self._graph_exec = None
+        self._io_graph_exec = None      # staging copies + the layers' launches + the output copy, as one graph
         self.kernel_launches_per_step = 0
 
     # ---- data movement helpers ----------------------------------------------------
@@ -203,6 +204,30 @@ class DecodeAttentionExecutor:
         finally:
             self.hip.programmatic_launch = False
 
+    def build_io_graph(self):
+        """One graph for a whole end-to-end step: kv offsets and every layer's Q from pinned
+        staging to the device, every layer's launches, every layer's output back to pinned
+        staging.  A step is then one graph launch instead of three copies and a launch (the
+        reference stages its offsets with a separate copy before each launch,
+        vte/core/hip_graph_executor.py:772-789)."""
+        if self._io_graph_exec is not None or not self.use_graph:
+            return
+        self.hip.programmatic_launch = self.programmatic
+        try:
+            self.hip.stream_begin_capture()
+            try:
+                self.hip.memcpy_h2d_async(ctypes.c_void_p(self.offsets.ptr), self._stage_offsets, 4 * self.B, "kv_offsets")
+                self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, self.L * self.q_bytes, "q staging")
+                self._record_all()
+                self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), self.L * self.out_bytes,
+                                          "attention output")
+            finally:
+                graph = self.hip.stream_end_capture()
+            self._io_graph_exec = self.hip.graph_instantiate(graph)
+            self.hip.graph_destroy(graph)
+        finally:
+            self.hip.programmatic_launch = False
+
     def _update_staging_buffers(self, kv_offsets: np.ndarray):
         off = np.ascontiguousarray(kv_offsets, dtype=np.int32)
         if off.shape != (self.B,):
@@ -229,19 +254,33 @@ class DecodeAttentionExecutor:
         Q [L,B,Hq,D] fp16) host -> device, replay the graph, read every layer's
         output back.  Returns [L,B,Hq,D] (fp32 or fp16)."""
         self.build_decode_graph()
-        self._update_staging_buffers(kv_offsets)
-        if q_host is not None:
+        nbytes = self.L * self.out_bytes
+        if q_host is not None and read_output and self.use_graph:
+            # the whole step as one graph launch
+            self.build_io_graph()
+            off = np.ascontiguousarray(kv_offsets, dtype=np.int32)
+            if off.shape != (self.B,) or off.min() < 0 or off.max() >= self.S:
+                raise CudaSafetyError(f"kv_offsets must be int32[{self.B}] within 0..{self.S - 1}")
             qh = np.ascontiguousarray(q_host, dtype=np.float16)
             if qh.nbytes != self.L * self.q_bytes:
                 raise CudaSafetyError("q_host must be [L, B, Hq, D] fp16")
+            ctypes.memmove(self._stage_offsets.value, off.ctypes.data, off.nbytes)
             ctypes.memmove(self._stage_q.value, qh.ctypes.data, qh.nbytes)
-            self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, qh.nbytes, "q staging")
-        self.launch_step()
-        if not read_output:
-            return None
-        nbytes = self.L * self.out_bytes
-        self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), nbytes, "attention output")
-        self.hip.stream_synchronize()
+            self.hip.graph_launch(self._io_graph_exec)
+            self.hip.stream_synchronize()
+        else:
+            self._update_staging_buffers(kv_offsets)
+            if q_host is not None:
+                qh = np.ascontiguousarray(q_host, dtype=np.float16)
+                if qh.nbytes != self.L * self.q_bytes:
+                    raise CudaSafetyError("q_host must be [L, B, Hq, D] fp16")
+                ctypes.memmove(self._stage_q.value, qh.ctypes.data, qh.nbytes)
+                self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, qh.nbytes, "q staging")
+            self.launch_step()
+            if not read_output:
+                return None
+            self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), nbytes, "attention output")
+            self.hip.stream_synchronize()
         self.dispatcher_check()
         dt = np.float32 if (self.output_f32 or self.emit_state) else np.float16
         flat = np.frombuffer((ctypes.c_char * nbytes).from_address(self._stage_out.value), dtype=dt)
@@ -270,6 +309,9 @@ class DecodeAttentionExecutor:
         if self._graph_exec is not None:
             self.hip.graph_exec_destroy(self._graph_exec)
             self._graph_exec = None
+        if self._io_graph_exec is not None:
+            self.hip.graph_exec_destroy(self._io_graph_exec)
+            self._io_graph_exec = None
         for p in (self._stage_offsets, self._stage_q, self._stage_out):
             if p is not None and p.value:
                 self.hip.host_free(p)
