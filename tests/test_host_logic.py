@@ -52,8 +52,8 @@ def test_plan_is_pure_host_arithmetic(built_library):
         small = FastPlan()
         assert lib.vteb_split_kv_plan_compact(hq, hkv, d, ctypes.byref(small)) == 0
         if small.ok:
-            assert small.threads == 192 and small.hg <= 4 and small.smem_bytes <= 227 * 1024 and small.nstages >= 2
-            assert small.hg * (2 if d == 256 else 1) <= 4
+            assert small.threads == 256 and small.hg <= 6 and small.smem_bytes <= 227 * 1024 and small.nstages >= 2
+            assert small.hg * (2 if d == 256 else 1) <= 6
     for hq, hkv, d in [(32, 2, 128), (12, 2, 96), (12, 5, 128), (12, 0, 128)]:   # group 16, odd dim, non-divisor
         plan = FastPlan()
         assert lib.vteb_split_kv_plan(hq, hkv, d, ctypes.byref(plan)) == 0
@@ -224,17 +224,17 @@ def test_compact_shape_selection():
     d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, variant="compact")
     assert d.compact and d.max_chunks == 148
     fp, ap, gp, bp, sp = d.build_launches(0, mapping(), 0x7200_0000_0000, batch=1)[1]
-    assert gp == (148, 1, 1) and bp == (192, 1, 1) and 100_000 < sp <= 227 * 1024
+    assert gp == (148, 1, 1) and bp == (256, 1, 1) and 100_000 < sp <= 227 * 1024
     assert [s for _, s in rt.loaded][1] == "vteb_split_kv_partial_compact_d128_kernel"
     # auto: compact for one sequence, full for a batch
     assert make_dispatcher(context_length=32768, batch_size=1, variant="auto")[0].compact
     assert not make_dispatcher(context_length=32768, batch_size=4, variant="auto")[0].compact
     assert not make_dispatcher(context_length=1 << 20, batch_size=1)[0].compact          # auto is the default
-    # 256-wide heads have a compact kernel too (two KV heads x two column halves = four warps)
+    # 256-wide heads have a compact kernel too (one KV head x two column halves x three block streams)
     wide = make_dispatcher({'attention.head_count': 8, 'attention.head_count_kv': 2, 'attention.key_length': 256},
                            variant="compact")[0]
     assert wide.compact
-    # eight 64-wide KV heads: four per item in the compact shape, eight in the full one
+    # eight 64-wide KV heads: four per item in the compact shape (six consumer warps), eight in the full one
     many = make_dispatcher({'attention.head_count': 32, 'attention.head_count_kv': 8, 'attention.key_length': 64},
                            variant="compact")[0]
     assert many.compact and many._plan.hg == 4 and many._plan.n_hgroups == 2

@@ -106,11 +106,11 @@ class SplitKVAttentionDispatcher:
         num_cus = hip.get_num_cus() if hip is not None and hasattr(hip, 'get_num_cus') else 32
         self.num_sms = num_cus
 
-        # CTA shape of the split kernel.  "full": 8 consumer + 2 loader warps.  "compact": 4 + 2
-        # warps, which leaves register-file room on every SM for the combine launch's CTAs to sit
-        # beside the split CTA, so the combine starts the moment the split ends and the launch after
-        # it is not held back.  Measured on B200, 32k context, one sequence: 11.4 us per layer compact
-        # against 13.6 us full, 8.7 against 10.8 at 512 positions; batches of ragged sequences and a
+        # CTA shape of the split kernel.  "full": 8 consumer + 2 loader warps.  "compact": 6 + 2
+        # warps of at most 160 registers, which leaves register-file room on every SM for the combine
+        # launch's CTAs to sit beside the split CTA, so the combine starts the moment the split ends
+        # and the launch after it is not held back.  Measured on B200, 32k context, one sequence:
+        # 10.6 us per layer compact against 12.5 us full; batches of ragged sequences and a
         # one-million-position sequence run 3 to 18 % slower compact (four warps do not keep up with
         # a stream that lasts hundreds of microseconds).  "auto" therefore takes compact for one
         # sequence of up to COMPACT_MAX_CONTEXT positions and full otherwise.

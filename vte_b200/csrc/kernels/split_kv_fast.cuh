@@ -1,7 +1,7 @@
 // Fast split kernel of the decode-attention path (included by decode_attention.cu).
 //
 // grid (n_ctas, 1, 1) persistent, block 320 = eight consumer warps + two loader
-// warps (192 = four + two in the compact shape), dynamic shared memory from
+// warps (256 = six + two in the compact shape), dynamic shared memory from
 // make_fast_plan().  A work item is one split
 // of one sequence for one group of `hg` KV heads; item t maps to
 // (sequence rank t / (n_hgroups * C), head group, split).  CTA i starts with
@@ -405,7 +405,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     const int hh = warp % plan.hg;                      // KV head within the group
     const int dhalf = (warp / plan.hg) % DS;            // which part of the output columns this warp owns
     const int sub = warp / (plan.hg * DS);              // which of the wph interleaved block streams
-    const int wph_mask = plan.wph - 1;    // wph is a power of two
+    int next_blk = sub;                   // index, within the item, of this warp's next block: sub, sub + wph, ...
     const int g = lane >> 2, t = lane & 3;
     const float scale2 = a.scale * kLog2e;
     constexpr int KS = D / 16;            // k-steps of the QK^T product
@@ -484,10 +484,10 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
 
         const uint32_t tile_base = smem_u32(stages + (size_t)stage * plan.stage_bytes);
-        for (int blk = 0; blk < blocks_per_tile; ++blk) {
-            const int r0 = blk * kBlockPos;
+        if (flags & kTileFirst) next_blk = sub;
+        for (; next_blk < blk0 + blocks_per_tile; next_blk += plan.wph) {
+            const int r0 = (next_blk - blk0) * kBlockPos;
             if (r0 >= nvalid) break;
-            if (((blk0 + blk) & wph_mask) != sub) continue;
             // ---- S = Q K^T: s[0] positions 0..7, s[1] positions 8..15; two accumulation
             // chains each; K fragments are fetched eight k-steps at a time
             const uint32_t kaddr = (tile_base + r0 * 128 + k_lane_off) | k_lane_x;
@@ -744,8 +744,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         combine_slice<true>(a.partial_m, a.partial_l, a.partial_o, a.output, a.out_kind, D, a.max_chunks, dsplit, slice, merge);
 }
 
-// compact shape: the register cap is what leaves room for the combine launch's CTAs on the same SM
-#define VTEB_COMPACT_BOUNDS __maxnreg__(168)
+// compact shape: the register cap (two warps per register-file partition, 5,120 registers each) is
+// what leaves room for the combine launch's CTAs on the same SM
+#define VTEB_COMPACT_BOUNDS __maxnreg__(160)
 
 #define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, BOUNDS)                                                  \
     extern "C" __global__ void BOUNDS NAME(                                                           \

@@ -12,17 +12,18 @@ namespace vteb {
 // Two shapes of the split kernel's CTA, both one CTA per SM with the whole shared memory
 // as K/V stages and two loader warps (K rows / V rows):
 //   full:    8 consumer warps, for work that keeps an SM busy for tens of microseconds;
-//   compact: 4 consumer warps.  Ten warps of 168 registers fill two of the SM's four
-//            register-file partitions, so no CTA of the combine kernel launched behind can
-//            become resident until a split CTA leaves, and the launch after that cannot
-//            even start until every combine CTA has.  Six warps leave room in every
-//            partition: the combine CTAs sit at their dependency wait while the split
-//            runs and the next layer's split is launched on time.  Measured at 32k
-//            context, one sequence: 11.4 us per layer against 13.6 us.
+//   compact: 6 consumer warps, at most 160 registers.  Ten warps of 168 registers fill two of
+//            the SM's four register-file partitions, so no CTA of the combine kernel launched
+//            behind can become resident until a split CTA leaves, and the launch after that
+//            cannot even start until every combine CTA has.  Eight warps of 160 registers
+//            (two per partition) leave 6 K registers free in every partition: the combine
+//            CTAs sit at their dependency wait while the split runs and the next layer's
+//            split is launched on time.  Measured at 32k context, one sequence: 10.6 us per
+//            layer against 12.5 us (4 consumer warps at 168 registers: 10.9 us; 6 at 168: 11.1 us).
 constexpr int kFullConsumerWarps = 8;
-constexpr int kCompactConsumerWarps = 4;
+constexpr int kCompactConsumerWarps = 6;
 constexpr int kFullThreads = (kFullConsumerWarps + 2) * 32;         // 320
-constexpr int kCompactThreads = (kCompactConsumerWarps + 2) * 32;   // 192
+constexpr int kCompactThreads = (kCompactConsumerWarps + 2) * 32;   // 256
 constexpr int kMaxStages = 8;
 constexpr int kBlockPos = 16;                            // positions per mma step
 constexpr float kLog2e = 1.4426950408889634f;
