@@ -42,7 +42,7 @@ NOMINAL_PEAK_TBS = 8.0
 # captures summarised in profiles/split_kv_partial_compact_d128_c2_32k_ncu.md (compact CTA shape,
 # the default for this workload) and profiles/split_kv_partial_d128_c2_32k_ncu.md (full shape);
 # same launch size as the bench's.
-NCU_TRAFFIC_BYTES = {("c2", True): 33612117, ("c2", False): 33603328}
+NCU_TRAFFIC_BYTES = {("c2", True): 33622699, ("c2", False): 33603328}
 
 
 def measured_peaks():
