@@ -172,6 +172,27 @@ def test_ragged_batch_matches_oracle(cuda_runtime, codegen):
     assert_parity(out2, ref, tight=5e-5)
 
 
+@pytest.mark.parametrize("shape", [(16, 32, 8, 64), (3, 12, 2, 128), (4, 8, 2, 256)], ids=["d64", "d128", "d256"])
+@pytest.mark.parametrize("variant", ["full", "compact"])
+def test_tensor_map_copies_and_16_byte_copies_give_the_same_bits(cuda_runtime, codegen, shape, variant):
+    """Whole tiles travel as tensor-map boxes, ragged ends as 16-byte copies; with tensor maps
+    off every tile takes the 16-byte path.  Both write the same shared-memory layout, so the
+    outputs and the partial buffers must be identical bit for bit."""
+    B, Hq, Hkv, D = shape
+    cfg = DecodeConfig("tma_vs_cp", 7, B, Hq, Hkv, D, 60, 1500, 1)
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    ref = orc.decode_attention(q, k, v, off)
+    got = {}
+    for tensor_maps in (True, False):
+        out, partials, C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=5, min_chunk=0,
+                                     variant=variant, tensor_maps=tensor_maps, strict_empty_splits=True)
+        assert_parity(out, ref, tight=5e-5)
+        got[tensor_maps] = (out, partials)
+    assert np.array_equal(got[True][0], got[False][0])
+    for a, b in zip(got[True][1], got[False][1]):
+        assert np.array_equal(a, b)
+
+
 def test_outlier_numerics_d256(cuda_runtime, codegen):
     """Config-4 shape at reduced size: sigma 0.5 with 1% x20 outliers stresses max / LSE."""
     cfg = DecodeConfig("c4_small", 4, 4, 8, 2, 256, 2048, 8192, 1, sigma_kv=0.5, outlier_frac=0.01, outlier_scale=20.0)
