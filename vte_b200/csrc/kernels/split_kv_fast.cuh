@@ -7,14 +7,16 @@
 // (sequence rank t / (n_hgroups * C), head group, split).  CTA i starts with
 // item i and draws the following ones from `*ticket` (gridDim.x + atomicAdd).
 //
-// Loader warp K (the first warp after the consumers): for every tile of `tile` positions it waits for a free
-// stage, writes the tile header, and copies the K rows (row_bytes contiguous
-// bytes covering the group's heads) with 16-byte asynchronous copies, one
-// 512-byte piece per warp instruction, into the 128-byte-swizzled tile layout.  Loader
-// warp V (warp 9) follows the headers and copies the V rows.  The copies'
-// completion is counted on the stage's "full" mbarrier.  Rows past the end of
-// the item are filled from the item's last row so that every row a consumer
-// touches holds finite numbers.
+// Loader warp K (the first warp after the consumers): for every tile of `tile` positions it
+// waits for a free stage, writes the tile header, and fetches the K rows (row_bytes contiguous
+// bytes covering the group's heads): a whole tile as tensor-map box copies issued by one lane
+// (one box of `tile` rows x 64 halves per 128-byte column block), a ragged tile with 16-byte
+// asynchronous copies, one 512-byte piece per warp instruction; both write the
+// 128-byte-swizzled tile layout.  Loader warp V (the next warp) follows the headers and
+// fetches the V rows.  Completion is counted on the stage's "full" mbarrier (transaction
+// bytes for the boxes, deferred arrivals for the 16-byte copies).  Rows past the end of the
+// item are filled from the item's last row so that every row a consumer touches holds finite
+// numbers.
 //
 // Consumer warp w: KV head (w % hg) of the group, every wph-th 16-position
 // block.  Per block: S = Q K^T with mma.sync m16n8k16 (Q rows are the query
