@@ -420,7 +420,7 @@ def run_kv_range(args, rank, world, local_rank, rdzv, cfg, n_layers):
                 "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
                 "config": config_json(cfg, args.workload, lengths, n_layers, n_layers, sh.ex.dispatcher.max_chunks, world,
                                       {"partition": f"KV range split over {world} GPUs, "
-                                                    + ("NCCL all-gather" if args.exchange == "nccl" else "peer stores over NVLink")
+                                                    + ("NCCL all-gather" if args.exchange == "nccl" else "tagged 64-bit peer stores over NVLink from the state combine" if sh.tagged else "peer stores over NVLink, then flags")
                                                     + f" of {sh.state_floats * 4} bytes per rank per layer",
                                        "input_generation": "device fill (counter-based normal)"}),
                 "us_per_layer_token": step_s * 1e6 / n_layers,
@@ -501,7 +501,7 @@ def main():
     ap.add_argument("--partition", default="", choices=["", "replicas", "sequences", "kv-range"],
                     help="with N > 1: replicas (each rank its own copy, weak; default), sequences (the batch is split "
                          "over the ranks, strong), kv-range (one sequence's KV range split over the ranks, NCCL all-gather)")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="kv-range partition: how the states travel")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-flags", "nccl"], help="kv-range partition: how the states travel")
     ap.add_argument("--balance", action="store_true",
                     help="sequences partition: give each rank the same number of sequences but pick them "
                          "longest-first onto the least loaded rank instead of contiguous blocks")

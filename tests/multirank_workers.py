@@ -88,8 +88,10 @@ def gpu_kv_shard_main():
     cfg = DecodeConfig("c5_small", 5, 1, 12, 2, 128, total, total, 2)
     meta = {'attention.head_count': 12, 'attention.head_count_kv': 2, 'attention.key_length': 128}
     lo, hi = kv_range_of_rank(total, rank, world)
-    sh = KVRangeShardedDecode(rt, CodegenEngine(), meta, hi - lo, cfg.layers, comm, num_splits=16, exchange=exchange,
+    sh = KVRangeShardedDecode(rt, CodegenEngine(), meta, hi - lo, cfg.layers, comm, num_splits=int(os.environ.get("VTEB_TEST_SPLITS", "16")), exchange=exchange,
                               rendezvous=rdzv)
+    if exchange == "p2p" and os.environ.get("VTEB_TEST_EXPECT_TAGGED") == "1":
+        assert sh.tagged, "expected the fused combine + push"
     refs = []
     for l in range(cfg.layers):
         q, k, v, off = make_layer_inputs(cfg, l)

@@ -59,6 +59,7 @@ class DecodeAttentionExecutor:
         self.with_append = bool(with_append)
         self.emit_state = bool(emit_state)          # outputs are [B, Hq, D + 2] fp32 shard states
         self.per_layer_hook = per_layer_hook        # called as hook(layer) after a layer's launches are recorded
+        self.launch_rewriter = None                 # optional: rewriter(layer, launches) -> launches, before recording
         self.kv_batch_stride = self.S * self.Hkv * self.D
         if self.kv_batch_stride >= 2 ** 31:
             raise CudaSafetyError("one sequence's cache exceeds 2^31 elements: the kernel ABI's stride is an int")
@@ -173,6 +174,8 @@ class DecodeAttentionExecutor:
             launches = self.dispatcher.build_launches(l, self.tensor_mapping, self.offsets.ptr, batch=self.B)
             if not self.with_append:
                 launches = launches[1:]
+            if self.launch_rewriter is not None:
+                launches = self.launch_rewriter(l, launches)
             if self.rope == "separate":
                 launches = [self.dispatcher.build_rope_launch(self.tensor_mapping, self.offsets.ptr, batch=self.B,
                                                               layer_idx=l)] + launches

@@ -40,11 +40,20 @@ class PeerTable(ctypes.Structure):
     _fields_ = [("board", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8)]
 
 
+class PairBoards(ctypes.Structure):
+    """Kernel argument of vteb_split_kv_combine_push_kernel: every rank's board of tagged
+    64-bit words as mapped into this process."""
+    _fields_ = [("board", ctypes.c_void_p * 8)]
+
+
 class KVRangeShardedDecode:
-    """`exchange="nccl"`: ncclAllGather of the states.  `exchange="p2p"`: every rank stores
-    its state into each peer's exported board over NVLink and the merge kernel waits
-    (bounded) for the peers' flags; needs `rendezvous` to swap the memory handles, at most
-    eight ranks, one process per GPU on one node."""
+    """`exchange="nccl"`: ncclAllGather of the states.  `exchange="p2p"`: the state combine itself
+    stores every value, as a 64-bit (value, step tag) word, into each rank's exported board over
+    NVLink, and the merge kernel polls (bounded) the words it needs on its own board: no fence,
+    no flag, one launch fewer per layer.  `exchange="p2p-flags"`: the earlier form, a push kernel
+    that stores the state and then raises a flag on every peer (also the fallback of "p2p" when
+    the short-list combine kernel is in use).  Both need `rendezvous` to swap the memory handles,
+    at most eight ranks, one process per GPU on one node."""
 
     def __init__(self, hip, codegen, metadata: dict, shard_context_length: int, n_layers: int, comm, *,
                  n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, programmatic: Optional[bool] = None,
@@ -52,9 +61,9 @@ class KVRangeShardedDecode:
         self.hip, self.comm = hip, comm
         self.world = comm.world if comm is not None else (rendezvous.world if rendezvous is not None else 1)
         self.rank = comm.rank if comm is not None else (rendezvous.rank if rendezvous is not None else 0)
-        if exchange not in ("nccl", "p2p"):
-            raise ValueError(f"exchange must be nccl or p2p, not {exchange!r}")
-        if exchange == "p2p" and (rendezvous is None or self.world > 8):
+        if exchange not in ("nccl", "p2p", "p2p-flags"):
+            raise ValueError(f"exchange must be nccl, p2p or p2p-flags, not {exchange!r}")
+        if exchange != "nccl" and (rendezvous is None or self.world > 8):
             raise ValueError("the p2p exchange needs the host rendezvous and at most eight ranks")
         self.exchange, self.rdzv = exchange, rendezvous
         self._peer_ptrs: list[int] = []
@@ -72,7 +81,8 @@ class KVRangeShardedDecode:
         arch = hip.get_gpu_architecture()
         _, self._merge_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_kernel')
         self._stage_merged = hip.host_alloc(self.L * self.rows * ex.D * 4)
-        if self.exchange == "p2p" and self.world > 1:
+        self.tagged = False                     # the fused combine + push with tagged words is in use
+        if self.exchange != "nccl" and self.world > 1:
             self._setup_peer_boards(codegen, arch)
 
     def _setup_peer_boards(self, codegen, arch):
@@ -81,7 +91,8 @@ class KVRangeShardedDecode:
         hip = self.hip
         self._board_floats = 2 * self.L * self.world * self.state_floats
         self._flag_ints = 2 * self.L * self.world
-        nbytes = self._board_floats * 4 + self._flag_ints * 4 + 64
+        board_bytes = self._board_floats * 8          # sized for 64-bit tagged words; the flag form uses half of it
+        nbytes = board_bytes + self._flag_ints * 4 + 64
         self._board = hip.safe_malloc(nbytes, "shard_states.board")
         hip.safe_memset(self._board, nbytes, "shard_states.board")
         hip.synchronize()
@@ -92,13 +103,22 @@ class KVRangeShardedDecode:
             if r != self.rank:
                 self._peer_ptrs.append(base)
             table.board[r] = base
-            table.flags[r] = base + self._board_floats * 4
+            table.flags[r] = base + board_bytes
         self._peers = table
-        self._flags_ptr = self._board.value + self._board_floats * 4
+        self._pair_boards = PairBoards()
+        for r in range(self.world):
+            self._pair_boards.board[r] = table.board[r]
+        self._flags_ptr = self._board.value + board_bytes
         self._step_ptr = self._flags_ptr + self._flag_ints * 4
         _, self._push_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_push_shard_state_kernel')
         _, self._merge_p2p_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_p2p_kernel')
         _, self._advance_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_advance_step_kernel')
+        _, self._combine_push_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_split_kv_combine_push_kernel')
+        _, self._merge_ll_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_ll_kernel')
+        # the fused form replaces the per-slice state combine; the short-list combine keeps the flag form
+        self.tagged = self.exchange == "p2p" and self.ex.dispatcher.max_chunks > 64 and self.ex.D <= 256
+        if self.tagged:
+            self.ex.launch_rewriter = self._fuse_push_into_combine
         self.rdzv.barrier()          # every board is zeroed and mapped before anyone pushes
 
     def _after_layer(self, l: int) -> int:
@@ -106,8 +126,8 @@ class KVRangeShardedDecode:
         ex = self.ex
         state_ptr = ex.out_all.ptr + l * ex.out_bytes
         gathered_ptr = self.gathered.ptr + l * self.world * self.state_floats * 4
-        if self.world > 1 and self.exchange == "p2p":
-            return self._after_layer_p2p(l, state_ptr)
+        if self.world > 1 and self.exchange != "nccl":
+            return self._after_layer_tagged(l) if self.tagged else self._after_layer_p2p(l, state_ptr)
         if self.world > 1:
             self.comm.all_gather_f32(state_ptr, gathered_ptr, self.state_floats)
         else:
@@ -121,6 +141,29 @@ class KVRangeShardedDecode:
         finally:
             self.hip.programmatic_launch = pdl
         return 2 if self.world > 1 else 1
+
+    def _fuse_push_into_combine(self, l: int, launches):
+        """Replaces layer l's state-combine launch (pm, pl, po, state, Hq, D, C, dsplit, ticket) by the
+        kernel that also stores the state into every rank's board."""
+        fn, args, grid, block, smem = launches[-1]
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        pm, pl, po, state, hq, d, c, dsplit, ticket = args
+        new_args = [pm, pl, po, state, self._pair_boards, hq, d, c, dsplit, ticket, ci(self.world), ci(self.rank), ci(l),
+                    ci(self.L), ci(self.rows), vp(self._step_ptr)]
+        return launches[:-1] + [(self._combine_push_fn, new_args, grid, block, smem)]
+
+    def _after_layer_tagged(self, l: int) -> int:
+        ex, hip = self.ex, self.hip
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        hip.launch_kernel_recorded(self._merge_ll_fn,
+                                   [vp(self._board.value), vp(self.merged.ptr + l * self.rows * ex.D * 4), ci(self.world),
+                                    ci(self.rows), ci(ex.D), ci(l), ci(self.L), vp(self._step_ptr),
+                                    vp(ex.dispatcher.work_ptr + 4)],
+                                   (self.rows, 1, 1), (ex.D, 1, 1), 0)
+        if l == self.L - 1:
+            hip.launch_kernel_recorded(self._advance_fn, [vp(self._step_ptr)], (1, 1, 1), (32, 1, 1), 0)
+            return 2
+        return 1
 
     def _after_layer_p2p(self, l: int, state_ptr: int) -> int:
         ex, hip = self.ex, self.hip

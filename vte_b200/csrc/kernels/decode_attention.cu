@@ -615,6 +615,41 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_state_ke
     fast_combine_kernel_body(partial_m, partial_l, partial_o, state, 3, head_dim, max_chunks, dsplit, ticket);
 }
 
+// Merges up to eight shard states of one query row: `st0` points at shard 0's row
+// ([head_dim] o, m, l), consecutive shards are `shard_stride` floats apart.  Every load of a
+// column is issued before any is used (one L2 round trip instead of one per shard).
+template <bool kBypassL1>
+__device__ __forceinline__ void merge_row_states(const float* __restrict__ st0, long long shard_stride, int n_shards,
+                                                 int head_dim, float* __restrict__ out_row)
+{
+    float mr[8], lr[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const float* st = st0 + r * shard_stride;
+        mr[r] = (r < n_shards) ? (kBypassL1 ? __ldcg(st + head_dim) : st[head_dim]) : kNeutralM;
+        lr[r] = (r < n_shards) ? (kBypassL1 ? __ldcg(st + head_dim + 1) : st[head_dim + 1]) : 0.f;
+    }
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float ov[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float* st = st0 + r * shard_stride;
+            ov[r] = (r < n_shards) ? (kBypassL1 ? __ldcg(st + d) : st[d]) : 0.f;
+        }
+        float M = kNeutralM;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) M = fmaxf(M, mr[r]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float w = (mr[r] <= -1e29f) ? 0.f : __expf(mr[r] - M);
+            acc = fmaf(ov[r], w, acc);
+            L = fmaf(lr[r], w, L);
+        }
+        out_row[d] = acc / fmaxf(L, 1e-20f);
+    }
+}
+
 // gathered: [n_shards][rows][D + 2]; out: [rows][D] fp32.  grid (rows, 1, 1), block (D, 1, 1).
 extern "C" __global__ void vteb_merge_shard_states_kernel(
     const float* __restrict__ gathered, float* __restrict__ out, int n_shards, int rows, int head_dim)
@@ -622,6 +657,11 @@ extern "C" __global__ void vteb_merge_shard_states_kernel(
     grid_launch_dependents();
     grid_dependency_wait();
     const int row = blockIdx.x, pitch = head_dim + 2;
+    if (n_shards <= 8) {
+        merge_row_states<false>(gathered + (long long)row * pitch, (long long)rows * pitch, n_shards, head_dim,
+                                out + (long long)row * head_dim);
+        return;
+    }
     float M = kNeutralM;
     for (int r = 0; r < n_shards; ++r) M = fmaxf(M, gathered[((long long)r * rows + row) * pitch + head_dim]);
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
@@ -714,6 +754,113 @@ extern "C" __global__ void vteb_merge_shard_states_p2p_kernel(
         }
         out[(long long)row * head_dim + d] = acc / fmaxf(L, 1e-20f);
     }
+}
+
+// ---------------------------------------------------------------------------
+// The exchange fused into the state combine ("LL" form): every value travels as an
+// 8-byte word (fp32 bits, tag = step + 1) written with one 64-bit store, so a word is
+// valid exactly when its tag matches and neither a fence nor a separate flag is needed.
+//   pairs: [2 parities][n_layers][world][state_floats] 64-bit words per rank's board
+// vteb_split_kv_combine_push_kernel = vteb_split_kv_combine_state_kernel (same grid, block
+// and shared memory) + peer stores of the slice each CTA produced, into every rank's board
+// (its own included).  vteb_merge_shard_states_ll_kernel polls (bounded) the words it needs
+// on the local board and merges.  Plain peer stores and local loads only.
+// ---------------------------------------------------------------------------
+struct VtebPairBoards {
+    unsigned long long* board[8];
+};
+
+__device__ __forceinline__ void store_tagged(unsigned long long* p, float v, int tag) {
+    const unsigned long long w = ((unsigned long long)(unsigned)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_tagged(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+
+extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_push_kernel(
+    const float* __restrict__ partial_m, const float* __restrict__ partial_l,
+    const float* __restrict__ partial_o, float* __restrict__ state, VtebPairBoards peers,
+    int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket,
+    int world, int rank, int layer, int n_layers, int rows, const int* __restrict__ step_word)
+{
+    extern __shared__ float combine_weight_sh[];   // [min(max_chunks, 256)]
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
+    combine_slice<false>(partial_m, partial_l, partial_o, state, 3, head_dim, max_chunks, dsplit, blockIdx.x,
+                         combine_weight_sh);
+    if (threadIdx.x < 32) {
+        // the first warp wrote this CTA's 32 columns (and m, l for column part 0) of the local state
+        __syncwarp();
+        const int bh = blockIdx.x / dsplit, dpart = blockIdx.x - bh * dsplit, pitch = head_dim + 2;
+        const int step = *step_word, tag = step + 1;
+        const long long state_floats = (long long)rows * pitch;
+        const long long slot = (((long long)(step & 1) * n_layers + layer) * world + rank) * state_floats;
+        const long long e = (long long)bh * pitch + dpart * 32 + threadIdx.x;
+        const float v = state[e];
+        const bool extra = dpart == 0 && threadIdx.x < 2;                   // m and l of the row
+        const long long e2 = (long long)bh * pitch + head_dim + threadIdx.x;
+        const float v2 = extra ? state[e2] : 0.f;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            if (p < world) {
+                store_tagged(peers.board[p] + slot + e, v, tag);
+                if (extra) store_tagged(peers.board[p] + slot + e2, v2, tag);
+            }
+        }
+    }
+}
+
+// grid (rows, 1, 1), block (D, 1, 1) with D <= 256.
+extern "C" __global__ void vteb_merge_shard_states_ll_kernel(
+    const unsigned long long* __restrict__ board, float* __restrict__ out, int world, int rows, int head_dim,
+    int layer, int n_layers, const int* __restrict__ step_word, int* __restrict__ status)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int step = *step_word;
+    const unsigned tag = (unsigned)(step + 1);
+    const int row = blockIdx.x, pitch = head_dim + 2, d = threadIdx.x;
+    const long long state_floats = (long long)rows * pitch;
+    const unsigned long long* base = board + (((long long)(step & 1) * n_layers + layer) * world) * state_floats +
+                                     (long long)row * pitch;
+    unsigned long long wo[8], wm[8], wl[8];
+    const long long t0 = clock64();
+    bool ok = true;
+    for (;;) {
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < world) {
+                const unsigned long long* st = base + r * state_floats;
+                wo[r] = (d < head_dim) ? load_tagged(st + d) : ((unsigned long long)tag << 32);
+                wm[r] = load_tagged(st + head_dim);
+                wl[r] = load_tagged(st + head_dim + 1);
+                all = all && (unsigned)(wo[r] >> 32) == tag && (unsigned)(wm[r] >> 32) == tag && (unsigned)(wl[r] >> 32) == tag;
+            }
+        }
+        if (all) break;
+        if (clock64() - t0 > 4000000000ll) { ok = false; break; }          // ~2 s: give up, report, return
+    }
+    if (!ok) { atomicCAS(status, 0, kStatusGridTimeout); return; }
+    if (d >= head_dim) return;
+    float M = kNeutralM;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) if (r < world) M = fmaxf(M, __uint_as_float((unsigned)wm[r]));
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        if (r < world) {
+            const float m = __uint_as_float((unsigned)wm[r]);
+            const float w = (m <= -1e29f) ? 0.f : __expf(m - M);
+            acc = fmaf(__uint_as_float((unsigned)wo[r]), w, acc);
+            L = fmaf(__uint_as_float((unsigned)wl[r]), w, L);
+        }
+    }
+    out[(long long)row * head_dim + d] = acc / fmaxf(L, 1e-20f);
 }
 
 // One thread: the decode step is over, the next one uses the other board parity.
