@@ -48,7 +48,7 @@ KERNEL_SIGNATURES = {
     "vteb_merge_shard_states_kernel": [P, P, I, I, I],
     "vteb_push_shard_state_kernel": [P, ctypes.Structure, I, I, I, I, I, P],
     "vteb_merge_shard_states_p2p_kernel": [P, P, P, I, I, I, I, I, P, P],
-    "vteb_split_kv_combine_push_kernel": [P, P, P, P, ctypes.Structure, I, I, I, I, P, I, I, I, I, I, P],
+    "vteb_split_kv_combine_push_kernel": [P, P, P, P, ctypes.Structure, I, I, I, I, P, I, I, I, I, I, P, P, P, P],
     "vteb_merge_shard_states_ll_kernel": [P, P, I, I, I, I, I, P, P],
     "vteb_advance_step_kernel": [P],
 }

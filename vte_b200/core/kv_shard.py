@@ -57,7 +57,7 @@ class KVRangeShardedDecode:
 
     def __init__(self, hip, codegen, metadata: dict, shard_context_length: int, n_layers: int, comm, *,
                  n_kv_buffers: Optional[int] = None, num_splits: Optional[int] = None, programmatic: Optional[bool] = None,
-                 exchange: str = "nccl", rendezvous=None):
+                 exchange: str = "nccl", rendezvous=None, fused_merge: bool = True):
         self.hip, self.comm = hip, comm
         self.world = comm.world if comm is not None else (rendezvous.world if rendezvous is not None else 1)
         self.rank = comm.rank if comm is not None else (rendezvous.rank if rendezvous is not None else 0)
@@ -66,6 +66,9 @@ class KVRangeShardedDecode:
         if exchange != "nccl" and (rendezvous is None or self.world > 8):
             raise ValueError("the p2p exchange needs the host rendezvous and at most eight ranks")
         self.exchange, self.rdzv = exchange, rendezvous
+        # "p2p" only: the combine launch also merges its slice of every rank's state (combine, exchange
+        # and merge in one kernel); False leaves the merge to a launch of its own
+        self.fused_merge = bool(fused_merge)
         self._peer_ptrs: list[int] = []
         self._board = None
         self.L = int(n_layers)
@@ -148,13 +151,21 @@ class KVRangeShardedDecode:
         fn, args, grid, block, smem = launches[-1]
         vp, ci = ctypes.c_void_p, ctypes.c_int
         pm, pl, po, state, hq, d, c, dsplit, ticket = args
+        merged = self.merged.ptr + l * self.rows * self.ex.D * 4 if self.fused_merge else 0
         new_args = [pm, pl, po, state, self._pair_boards, hq, d, c, dsplit, ticket, ci(self.world), ci(self.rank), ci(l),
-                    ci(self.L), ci(self.rows), vp(self._step_ptr)]
+                    ci(self.L), ci(self.rows), vp(self._step_ptr), vp(self._board.value), vp(merged),
+                    vp(self.ex.dispatcher.work_ptr + 4)]
         return launches[:-1] + [(self._combine_push_fn, new_args, grid, block, smem)]
 
     def _after_layer_tagged(self, l: int) -> int:
         ex, hip = self.ex, self.hip
         vp, ci = ctypes.c_void_p, ctypes.c_int
+        if self.fused_merge:
+            # the combine launch merged as well: nothing to add but the step advance
+            if l == self.L - 1:
+                hip.launch_kernel_recorded(self._advance_fn, [vp(self._step_ptr)], (1, 1, 1), (32, 1, 1), 0)
+                return 1
+            return 0
         hip.launch_kernel_recorded(self._merge_ll_fn,
                                    [vp(self._board.value), vp(self.merged.ptr + l * self.rows * ex.D * 4), ci(self.world),
                                     ci(self.rows), ci(ex.D), ci(l), ci(self.L), vp(self._step_ptr),

@@ -763,8 +763,10 @@ extern "C" __global__ void vteb_merge_shard_states_p2p_kernel(
 //   pairs: [2 parities][n_layers][world][state_floats] 64-bit words per rank's board
 // vteb_split_kv_combine_push_kernel = vteb_split_kv_combine_state_kernel (same grid, block
 // and shared memory) + peer stores of the slice each CTA produced, into every rank's board
-// (its own included).  vteb_merge_shard_states_ll_kernel polls (bounded) the words it needs
-// on the local board and merges.  Plain peer stores and local loads only.
+// (its own included) + that slice of the merge: the CTA's first warp polls (bounded) the same
+// 32 columns and the row's m, l of every rank on the local board and stores the merged,
+// normalised output.  With `merged_out` null the merge is left to
+// vteb_merge_shard_states_ll_kernel.  Plain peer stores and local loads only.
 // ---------------------------------------------------------------------------
 struct VtebPairBoards {
     unsigned long long* board[8];
@@ -780,11 +782,13 @@ __device__ __forceinline__ unsigned long long load_tagged(const unsigned long lo
     return w;
 }
 
-extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_push_kernel(
+// (capped at 80 registers so that its CTAs still fit beside a compact split CTA)
+extern "C" __global__ void __maxnreg__(80) vteb_split_kv_combine_push_kernel(
     const float* __restrict__ partial_m, const float* __restrict__ partial_l,
     const float* __restrict__ partial_o, float* __restrict__ state, VtebPairBoards peers,
     int num_q_heads, int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket,
-    int world, int rank, int layer, int n_layers, int rows, const int* __restrict__ step_word)
+    int world, int rank, int layer, int n_layers, int rows, const int* __restrict__ step_word,
+    const unsigned long long* __restrict__ local_board, float* __restrict__ merged_out, int* __restrict__ status)
 {
     extern __shared__ float combine_weight_sh[];   // [min(max_chunks, 256)]
     grid_launch_dependents();
@@ -792,26 +796,63 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_push_ker
     if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
     combine_slice<false>(partial_m, partial_l, partial_o, state, 3, head_dim, max_chunks, dsplit, blockIdx.x,
                          combine_weight_sh);
-    if (threadIdx.x < 32) {
-        // the first warp wrote this CTA's 32 columns (and m, l for column part 0) of the local state
-        __syncwarp();
-        const int bh = blockIdx.x / dsplit, dpart = blockIdx.x - bh * dsplit, pitch = head_dim + 2;
-        const int step = *step_word, tag = step + 1;
-        const long long state_floats = (long long)rows * pitch;
-        const long long slot = (((long long)(step & 1) * n_layers + layer) * world + rank) * state_floats;
-        const long long e = (long long)bh * pitch + dpart * 32 + threadIdx.x;
-        const float v = state[e];
-        const bool extra = dpart == 0 && threadIdx.x < 2;                   // m and l of the row
-        const long long e2 = (long long)bh * pitch + head_dim + threadIdx.x;
-        const float v2 = extra ? state[e2] : 0.f;
+    if (threadIdx.x >= 32) return;
+    // the first warp wrote this CTA's 32 columns (and m, l for column part 0) of the local state
+    __syncwarp();
+    const int bh = blockIdx.x / dsplit, dpart = blockIdx.x - bh * dsplit, pitch = head_dim + 2;
+    const int step = *step_word, tag = step + 1;
+    const long long state_floats = (long long)rows * pitch;
+    const long long layer_slot = ((long long)(step & 1) * n_layers + layer) * world * state_floats;
+    const long long slot = layer_slot + (long long)rank * state_floats;
+    const long long e = (long long)bh * pitch + dpart * 32 + threadIdx.x;
+    const long long em = (long long)bh * pitch + head_dim;
+    const float v = state[e];
+    const bool extra = dpart == 0 && threadIdx.x < 2;                       // m and l of the row
+    const float v2 = extra ? state[em + threadIdx.x] : 0.f;
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-            if (p < world) {
-                store_tagged(peers.board[p] + slot + e, v, tag);
-                if (extra) store_tagged(peers.board[p] + slot + e2, v2, tag);
-            }
+    for (int p = 0; p < 8; ++p) {
+        if (p < world) {
+            store_tagged(peers.board[p] + slot + e, v, tag);
+            if (extra) store_tagged(peers.board[p] + slot + em + threadIdx.x, v2, tag);
         }
     }
+    if (merged_out == nullptr) return;             // the merge runs as a launch of its own
+    // ---- this CTA's slice of the merge: the same 32 columns (and the row's m, l) of every rank,
+    // read from the local board as they arrive
+    unsigned long long wo[8], wm[8], wl[8];
+    const long long t0 = clock64();
+    bool ok = true;
+    for (;;) {
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < world) {
+                const unsigned long long* st = local_board + layer_slot + r * state_floats;
+                wo[r] = load_tagged(st + e);
+                wm[r] = load_tagged(st + em);
+                wl[r] = load_tagged(st + em + 1);
+                all = all && (unsigned)(wo[r] >> 32) == (unsigned)tag && (unsigned)(wm[r] >> 32) == (unsigned)tag &&
+                      (unsigned)(wl[r] >> 32) == (unsigned)tag;
+            }
+        }
+        if (all) break;
+        if (clock64() - t0 > 4000000000ll) { ok = false; break; }          // ~2 s: give up, report, return
+    }
+    if (!ok) { atomicCAS(status, 0, kStatusGridTimeout); return; }
+    float M = kNeutralM;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) if (r < world) M = fmaxf(M, __uint_as_float((unsigned)wm[r]));
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        if (r < world) {
+            const float m = __uint_as_float((unsigned)wm[r]);
+            const float w = (m <= -1e29f) ? 0.f : __expf(m - M);
+            acc = fmaf(__uint_as_float((unsigned)wo[r]), w, acc);
+            L = fmaf(__uint_as_float((unsigned)wl[r]), w, L);
+        }
+    }
+    merged_out[(long long)bh * head_dim + dpart * 32 + threadIdx.x] = acc / fmaxf(L, 1e-20f);
 }
 
 // grid (rows, 1, 1), block (D, 1, 1) with D <= 256.
