@@ -220,6 +220,67 @@ def test_rope_cache_builder_matches_the_pinned_tables():
         assert np.array_equal(cos[:, :width // 2], cos[:, width // 2:])
 
 
+def test_tensor_maps_are_passed_when_the_cache_is_a_matrix_of_rows():
+    from vte_b200.bridge.cuda_runtime import KvTensorMap
+    from vte_b200.core.split_kv_attention import FLAG_TENSOR_MAPS
+
+    class MapRuntime(FakeRuntime):
+        def __init__(self):
+            super().__init__()
+            self.encoded = []
+        def kv_tensor_map(self, ptr, n_rows, row_halves, box_rows):
+            self.encoded.append((ptr, n_rows, row_halves, box_rows))
+            tm = KvTensorMap()
+            tm.opaque[0] = ptr
+            return tm
+
+    rt = MapRuntime()
+    alloc = SlabAllocator(rt, 180 << 30, requested_pool_size=1 << 30)
+    alloc.initialize()
+    meta = {'attention.head_count': 12, 'attention.head_count_kv': 2, 'attention.key_length': 128}
+    d = SplitKVAttentionDispatcher(rt, FakeCodegen(), meta, allocator=alloc, context_length=32768, batch_size=1)
+    m = mapping()
+    ap = d.build_launches(0, m, 0x7200_0000_0000, batch=1)[1][1]
+    assert ap[15].value & FLAG_TENSOR_MAPS
+    assert ap[23].opaque[0] == m['blk.0.kv_cache.k'] and ap[24].opaque[0] == m['blk.0.kv_cache.v']
+    # rows = stride / (Hkv * D), boxes of `tile` rows; encoded once per cache, reused on the next capture
+    assert rt.encoded == [(m['blk.0.kv_cache.k'], 32768, 256, d._plan.tile), (m['blk.0.kv_cache.v'], 32768, 256, d._plan.tile)]
+    d.build_launches(0, m, 0x7200_0000_0000, batch=1)
+    assert len(rt.encoded) == 2
+    # a sequence stride that is not a whole number of position rows: 16-byte copies only
+    odd = dict(m, kv_batch_stride_elements=32768 * 256 + 8)
+    ap2 = d.build_launches(0, odd, 0x7200_0000_0000, batch=1)[1][1]
+    assert not (ap2[15].value & FLAG_TENSOR_MAPS) and ap2[23].opaque[0] == 0
+    # switched off by the caller
+    d2 = SplitKVAttentionDispatcher(rt, FakeCodegen(), meta, allocator=alloc, context_length=32768, batch_size=1,
+                                    tensor_maps=False)
+    assert not (d2.build_launches(0, m, 0x7200_0000_0000, batch=1)[1][1][15].value & FLAG_TENSOR_MAPS)
+
+
+def test_kv_range_combine_launch_is_rewritten_for_the_fused_exchange():
+    from vte_b200.core.kv_shard import KVRangeShardedDecode, PairBoards
+    sh = object.__new__(KVRangeShardedDecode)
+    sh.world, sh.rank, sh.L, sh.rows, sh.fused_merge = 4, 2, 28, 12, True
+    sh._pair_boards, sh._step_ptr, sh._combine_push_fn = PairBoards(), 0x7400_0000_0040, ctypes.c_void_p(0x99)
+    sh._board = ctypes.c_void_p(0x7400_0000_0000)
+    class Ex: D = 128
+    class Disp: work_ptr = 0x7500_0000_0000
+    class Merged: ptr = 0x7600_0000_0000
+    Ex.dispatcher = Disp; sh.ex = Ex; sh.merged = Merged
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    combine = ("combine_fn", [vp(1), vp(2), vp(3), vp(4), ci(12), ci(128), ci(148), ci(4), vp(5)], (48, 1, 1), (256, 1, 1), 592)
+    out = sh._fuse_push_into_combine(3, ["append", "split", combine])
+    assert out[:2] == ["append", "split"]
+    fn, args, grid, block, smem = out[2]
+    assert fn is sh._combine_push_fn and (grid, block, smem) == ((48, 1, 1), (256, 1, 1), 592)
+    sig = KERNEL_SIGNATURES["vteb_split_kv_combine_push_kernel"]
+    assert len(args) == len(sig) == 19 and all(isinstance(a, t) for a, t in zip(args, sig))
+    assert [a.value for a in args[10:15]] == [4, 2, 3, 28, 12]
+    assert args[17].value == Merged.ptr + 3 * 12 * 128 * 4 and args[18].value == Disp.work_ptr + 4
+    sh.fused_merge = False
+    assert sh._fuse_push_into_combine(3, [combine])[0][1][17].value in (0, None)
+
+
 def test_compact_shape_selection():
     d, rt, cg, _ = make_dispatcher(context_length=32768, batch_size=1, variant="compact")
     assert d.compact and d.max_chunks == 148
