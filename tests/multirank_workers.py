@@ -89,7 +89,7 @@ def gpu_kv_shard_main():
     meta = {'attention.head_count': 12, 'attention.head_count_kv': 2, 'attention.key_length': 128}
     lo, hi = kv_range_of_rank(total, rank, world)
     sh = KVRangeShardedDecode(rt, CodegenEngine(), meta, hi - lo, cfg.layers, comm, num_splits=int(os.environ.get("VTEB_TEST_SPLITS", "16")), exchange=exchange,
-                              rendezvous=rdzv)
+                              rendezvous=rdzv, fused_merge=os.environ.get("VTEB_TEST_FUSED_MERGE", "1") == "1")
     if exchange == "p2p" and os.environ.get("VTEB_TEST_EXPECT_TAGGED") == "1":
         assert sh.tagged, "expected the fused combine + push"
     refs = []

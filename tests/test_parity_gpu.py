@@ -319,9 +319,10 @@ def test_kv_range_shards_merge_to_the_full_result(cuda_runtime, codegen):
         sh.cleanup()
 
 
-@pytest.mark.parametrize("exchange,splits", [("nccl", 16), ("p2p", 80), ("p2p", 16), ("p2p-flags", 80)],
-                         ids=["nccl", "p2p-tagged", "p2p-short-list", "p2p-flags"])
-def test_two_gpu_kv_range_sharding(cuda_runtime, exchange, splits):
+@pytest.mark.parametrize("exchange,splits,fused_merge",
+                         [("nccl", 16, 1), ("p2p", 80, 1), ("p2p", 80, 0), ("p2p", 16, 1), ("p2p-flags", 80, 1)],
+                         ids=["nccl", "p2p-one-kernel", "p2p-tagged-separate-merge", "p2p-short-list", "p2p-flags"])
+def test_two_gpu_kv_range_sharding(cuda_runtime, exchange, splits, fused_merge):
     """Two ranks, one process per GPU; the shard states travel by NCCL all-gather, by tagged
     64-bit peer stores issued by the state combine itself, or by a push kernel that raises flags
     (which is also what "p2p" falls back to when the short-list combine is in use).
@@ -338,7 +339,8 @@ def test_two_gpu_kv_range_sharding(cuda_runtime, exchange, splits):
     for r in range(2):
         env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", VTEB_TEST_EXCHANGE=exchange,
-                   VTEB_TEST_SPLITS=str(splits), VTEB_TEST_EXPECT_TAGGED="1" if splits > 64 else "0")
+                   VTEB_TEST_SPLITS=str(splits), VTEB_TEST_EXPECT_TAGGED="1" if splits > 64 else "0",
+                   VTEB_TEST_FUSED_MERGE=str(fused_merge))
         procs.append(subprocess.Popen([sys.executable, str(Path(__file__).parent / "multirank_workers.py")], env=env,
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=240)[0] for p in procs]
