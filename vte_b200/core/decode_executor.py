@@ -15,6 +15,7 @@ Unlike the reference's batched executor it admits ragged context lengths.
 from __future__ import annotations
 
 import ctypes
+import types
 from typing import Optional
 
 import numpy as np
@@ -23,6 +24,10 @@ from ..bridge.errors import CudaSafetyError
 from ..bridge.memory import MemoryRegion, SlabAllocator
 from ..config import ENV_NO_PDL, env_flag
 from .split_kv_attention import SplitKVAttentionDispatcher
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
 
 
 class DecodeAttentionExecutor:
@@ -75,27 +80,32 @@ class DecodeAttentionExecutor:
         self._owns_allocator = allocator is None
         if allocator is None:
             need = (2 * self.n_kv * (self.kv_bytes + 256) + self.L * (self.q_bytes + 2 * self.kvnew_bytes
-                    + self.out_bytes + 1024) + (64 << 20) + (4 * self.S * self.D + 4096 if rope != "off" else 0))
+                    + self.out_bytes + 1024) + (64 << 20) + 4 * self.B + 4096 + (4 * self.S * self.D + 4096 if rope != "off" else 0))
             free_b, total_b = hip.get_real_mem_info()
             allocator = SlabAllocator(hip, total_b, requested_pool_size=need)
             allocator.initialize()
         self.allocator = allocator
+        A = allocator.allocate
+        # Every layer's Q, then the kv offsets, in one allocation; every layer's output, then the
+        # dispatcher's work words (ticket, status), in another: an end-to-end step is then one copy in
+        # and one copy out, and the status word comes back with the results.
+        self._q_tail = _round_up(self.L * self.q_bytes, 256)
+        self._out_tail = _round_up(self.L * self.out_bytes, 256)
+        self.q_all = A(self._q_tail + _round_up(4 * self.B, 256), "q_proj.output.all", MemoryRegion.ACTIVATIONS)
+        self.out_all = A(self._out_tail + 256, "attention.output.all", MemoryRegion.ACTIVATIONS)
+        self.offsets = types.SimpleNamespace(ptr=self.q_all.ptr + self._q_tail, size=4 * self.B)
         self.dispatcher = SplitKVAttentionDispatcher(
             hip, codegen, self.metadata, allocator=allocator, context_length=self.S, batch_size=self.B,
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
             prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant,
-            fuse_rope=(rope == "fused"), tensor_maps=tensor_maps)
+            fuse_rope=(rope == "fused"), tensor_maps=tensor_maps, work_ptr=self.out_all.ptr + self._out_tail)
 
-        A = allocator.allocate
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
         self.v_cache = [A(self.kv_bytes, f"kv_cache.v.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
         # all layers' Q (and outputs) are contiguous so one copy moves a whole step's worth
-        self.q_all = A(self.L * self.q_bytes, "q_proj.output.all", MemoryRegion.ACTIVATIONS)
         self.knew_all = A(self.L * self.kvnew_bytes, "k_proj.output.all", MemoryRegion.ACTIVATIONS)
         self.vnew_all = A(self.L * self.kvnew_bytes, "v_proj.output.all", MemoryRegion.ACTIVATIONS)
-        self.out_all = A(self.L * self.out_bytes, "attention.output.all", MemoryRegion.ACTIVATIONS)
-        self.offsets = A(4 * self.B, "kv_offsets", MemoryRegion.ACTIVATIONS)
 
         self.tensor_mapping = {'kv_batch_stride_elements': self.kv_batch_stride}
         for l in range(self.L):
@@ -119,9 +129,10 @@ class DecodeAttentionExecutor:
             self.tensor_mapping['rope_sin'] = self.rope_sin
 
         # pinned staging: offsets, a step's Q, a step's outputs
-        self._stage_offsets = hip.host_alloc(4 * self.B)
-        self._stage_q = hip.host_alloc(self.L * self.q_bytes)
-        self._stage_out = hip.host_alloc(self.L * self.out_bytes)
+        self._stage_q = hip.host_alloc(self._q_tail + _round_up(4 * self.B, 256))          # Q of every layer, then the offsets
+        self._stage_offsets = ctypes.c_void_p(self._stage_q.value + self._q_tail)
+        self._stage_out = hip.host_alloc(self._out_tail + 256)                               # outputs, then the work words
+        ctypes.memset(self._stage_out.value, 0, self._out_tail + 256)
         self._graph_exec = None
         self._io_graph_exec = None      # staging copies + the layers' launches + the output copy, as one graph
         self.kernel_launches_per_step = 0
@@ -219,11 +230,11 @@ class DecodeAttentionExecutor:
         try:
             self.hip.stream_begin_capture()
             try:
-                self.hip.memcpy_h2d_async(ctypes.c_void_p(self.offsets.ptr), self._stage_offsets, 4 * self.B, "kv_offsets")
-                self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, self.L * self.q_bytes, "q staging")
+                self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, self._q_tail + 4 * self.B,
+                                          "q and kv offsets staging")
                 self._record_all()
-                self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), self.L * self.out_bytes,
-                                          "attention output")
+                self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), self._out_tail + 16,
+                                          "attention output and status word")
             finally:
                 graph = self.hip.stream_end_capture()
             self._io_graph_exec = self.hip.graph_instantiate(graph)
@@ -271,6 +282,10 @@ class DecodeAttentionExecutor:
             ctypes.memmove(self._stage_q.value, qh.ctypes.data, qh.nbytes)
             self.hip.graph_launch(self._io_graph_exec)
             self.hip.stream_synchronize()
+            # the status word travelled with the outputs: only a non-zero one needs the slow path
+            if ctypes.c_int.from_address(self._stage_out.value + self._out_tail + 4).value != 0:
+                self.dispatcher_check()
+            return self._output_array(nbytes)
         else:
             self._update_staging_buffers(kv_offsets)
             if q_host is not None:
@@ -285,6 +300,9 @@ class DecodeAttentionExecutor:
             self.hip.memcpy_d2h_async(self._stage_out, ctypes.c_void_p(self.out_all.ptr), nbytes, "attention output")
             self.hip.stream_synchronize()
         self.dispatcher_check()
+        return self._output_array(nbytes)
+
+    def _output_array(self, nbytes: int) -> np.ndarray:
         dt = np.float32 if (self.output_f32 or self.emit_state) else np.float16
         flat = np.frombuffer((ctypes.c_char * nbytes).from_address(self._stage_out.value), dtype=dt)
         return flat.reshape(self.L, self.B, self.Hq, self.D + 2 if self.emit_state else self.D).copy()
@@ -315,7 +333,7 @@ class DecodeAttentionExecutor:
         if self._io_graph_exec is not None:
             self.hip.graph_exec_destroy(self._io_graph_exec)
             self._io_graph_exec = None
-        for p in (self._stage_offsets, self._stage_q, self._stage_out):
+        for p in (self._stage_q, self._stage_out):
             if p is not None and p.value:
                 self.hip.host_free(p)
         self._stage_offsets = self._stage_q = self._stage_out = None

@@ -84,7 +84,7 @@ class SplitKVAttentionDispatcher:
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
                  strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True,
                  fused_combine: bool | None = None, variant: str = "auto", fuse_rope: bool = False,
-                 tensor_maps: bool = True):
+                 tensor_maps: bool = True, work_ptr: int | None = None):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -185,6 +185,11 @@ class SplitKVAttentionDispatcher:
         self.tensor_maps = bool(tensor_maps) and hip is not None and hasattr(hip, 'kv_tensor_map')
         self._tensor_map_cache = {}
 
+        # work_ptr: 16 bytes of device memory for the work words (ticket, status) supplied by the
+        # caller, e.g. next to its output buffer so that one copy brings the status word back with the
+        # results; by default they come from the allocator with the other scratch
+        self._external_work_ptr = int(work_ptr) if work_ptr else None
+
         self._kernel_cache = {}
         self._rows_combine = False
         self._partial_m = self._partial_l = self._partial_o = self._work = None
@@ -254,7 +259,11 @@ class SplitKVAttentionDispatcher:
             self._partial_l = self.allocator.allocate(stats_size, "attn_splitkv_l", MemoryRegion.SCRATCH)
             self._partial_o = self.allocator.allocate(o_size, "attn_splitkv_o", MemoryRegion.SCRATCH)
             # work[0]: work-queue ticket (zero between launches), work[1]: status word
-            self._work = self.allocator.allocate(16, "attn_splitkv_work", MemoryRegion.SCRATCH)
+            if self._external_work_ptr is not None:
+                import types
+                self._work = types.SimpleNamespace(ptr=self._external_work_ptr, size=16)
+            else:
+                self._work = self.allocator.allocate(16, "attn_splitkv_work", MemoryRegion.SCRATCH)
             if hasattr(self.hip, 'safe_memset'):
                 self.hip.safe_memset(ctypes.c_void_p(self._work.ptr), 16, "attn_splitkv_work")
         return self._kernel_cache['append'], self._kernel_cache['partial'], self._kernel_cache['reduce']
