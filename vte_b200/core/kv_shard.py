@@ -84,6 +84,7 @@ class KVRangeShardedDecode:
         arch = hip.get_gpu_architecture()
         _, self._merge_fn = codegen.load_kernel_safe(hip, 'decode_attention', arch, 'vteb_merge_shard_states_kernel')
         self._stage_merged = hip.host_alloc(self.L * self.rows * ex.D * 4)
+        self._stage_status = hip.host_alloc(64)          # the split kernels' status word, read back with the result
         self.tagged = False                     # the fused combine + push with tagged words is in use
         if self.exchange != "nccl" and self.world > 1:
             self._setup_peer_boards(codegen, arch)
@@ -207,8 +208,10 @@ class KVRangeShardedDecode:
         ex.launch_step()
         nbytes = self.L * self.rows * ex.D * 4
         self.hip.memcpy_d2h_async(self._stage_merged, ctypes.c_void_p(self.merged.ptr), nbytes, "attention output merged")
+        self.hip.memcpy_d2h_async(self._stage_status, ctypes.c_void_p(ex.dispatcher.work_ptr + 4), 4, "status word output")
         self.hip.stream_synchronize()
-        ex.dispatcher_check()
+        if ctypes.c_int.from_address(self._stage_status.value).value != 0:
+            ex.dispatcher_check()                       # raises with the reason and clears the word
         flat = np.frombuffer((ctypes.c_char * nbytes).from_address(self._stage_merged.value), dtype=np.float32)
         return flat.reshape(self.L, ex.Hq, ex.D).copy()
 
@@ -227,5 +230,6 @@ class KVRangeShardedDecode:
             self._board = None
         if self._stage_merged is not None and self._stage_merged.value:
             self.hip.host_free(self._stage_merged)
+            self.hip.host_free(self._stage_status)
             self._stage_merged = None
         self.ex.cleanup()
