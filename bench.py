@@ -327,7 +327,8 @@ def run_ours(args, rank, world, local_rank):
                                    "combine": "inside the split launch (grid barrier)" if ex.dispatcher.fused_combine else "separate launch", "kernels": "compat" if args.compat else ("fast, compact CTAs" if ex.dispatcher.compact else "fast, full CTAs"),
                                    "step_contents": {"off": "split + combine per layer",
                                                      "separate": "rotation launch + cache append + split + combine per layer",
-                                                     "fused": "cache append with K rotation + split with Q rotation + combine per layer"}[args.rope]}),
+                                                     "fused": "cache append with K rotation + split with Q rotation + combine per layer",
+                                                     "fused-append": "split (with Q rotation, K rotation and the cache append) + combine per layer"}[args.rope]}),
             "us_per_layer_token": step_s * 1e6 / n_layers / global_cfg.batch,
             "pct_of_nominal_8TBs": 100.0 * value / world / NOMINAL_PEAK_TBS,
             "pct_of_measured_copy": 100.0 * value / world / (peak_gbs / 1e3),
@@ -449,7 +450,7 @@ def kernel_durations(rt, ex, n_layers, reps=10):
     includes the in-graph launch gap between consecutive kernels."""
     disp = ex.dispatcher
     name = ("flash_attention_split_kv_partial_kernel" if disp.compat else
-            f"vteb_split_kv_partial_{'compact_' if disp.compact else ''}{'rope_' if disp.fuse_rope else ''}d{disp.head_dim}_kernel")
+            f"vteb_split_kv_partial_{'compact_' if disp.compact else ''}{'rope_' if (disp.fuse_rope or disp.fuse_append) else ''}d{disp.head_dim}_kernel")
     out = {}
     kinds = ((0, "split_us"),) if disp.fused_combine else ((0, "split_us"), (1, "combine_us"))
     out["combine_us"] = 0.0
@@ -457,7 +458,9 @@ def kernel_durations(rt, ex, n_layers, reps=10):
         rt.stream_begin_capture()
         try:
             for l in range(n_layers):
-                launches = disp.build_launches(l, ex.tensor_mapping, ex.offsets.ptr, batch=ex.B)[1:]
+                launches = disp.build_launches(l, ex.tensor_mapping, ex.offsets.ptr, batch=ex.B)
+                if not disp.fuse_append:
+                    launches = launches[1:]                     # drop the append launch
                 fn, args, grid, block, smem = launches[which]
                 if (which == 0 and not disp.compat and not disp.fused_combine
                         and ex.B * disp._plan.n_hgroups * disp.max_chunks > grid[0]):
@@ -511,7 +514,7 @@ def main():
     ap.add_argument("--no-prefetch", action="store_true", help="do not prefetch the next layer's KV into L2")
     ap.add_argument("--compat", action="store_true", help="time the reference-geometry kernels")
     ap.add_argument("--no-tma", action="store_true", help="fetch every K/V tile with 16-byte asynchronous copies (no tensor-map copies)")
-    ap.add_argument("--rope", default="off", choices=["off", "separate", "fused"],
+    ap.add_argument("--rope", default="off", choices=["off", "separate", "fused", "fused-append"],
                     help="also run the rotary embedding and the cache append inside the step: as the standalone "
                          "rotation launch, or folded into the append (K) and the split kernel's Q load")
     ap.add_argument("--device-fill", action="store_true")

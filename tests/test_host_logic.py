@@ -186,9 +186,10 @@ def test_fused_rope_launch_list_and_standalone_rotation_launch():
     assert symbols[:2] == ["kv_cache_append_rope_kernel", "vteb_split_kv_partial_rope_d256_kernel"]
     (fa, aa, ga, ba, sa), (fp, ap, gp, bp, sp) = launches[:2]
     assert len(aa) == len(KERNEL_SIGNATURES["kv_cache_append_rope_kernel"]) == 12
-    assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_rope_d256_kernel"]) == 29
-    for args in (aa, ap):
-        assert [a.value for a in args[-4:]] == [0x7300_0000_0000, 0x7300_1000_0000, 2, 64]
+    assert len(ap) == len(KERNEL_SIGNATURES["vteb_split_kv_partial_rope_d256_kernel"]) == 31
+    assert [a.value for a in aa[-4:]] == [0x7300_0000_0000, 0x7300_1000_0000, 2, 64]
+    assert [a.value for a in ap[-6:-2]] == [0x7300_0000_0000, 0x7300_1000_0000, 2, 64]
+    assert [a.value for a in ap[-2:]] in ([0, 0], [None, None])           # no fused append asked for
     assert ga == (4, 2, 1) and ba == (256, 1, 1)
     # the standalone launch: the reference's eleven arguments and its grid rule
     fn, args, grid, block, smem = d.build_rope_launch(m, 0x7200_0000_0000, batch=4)
@@ -201,8 +202,19 @@ def test_fused_rope_launch_list_and_standalone_rotation_launch():
         make_dispatcher(meta128, fuse_rope=True, compat=True)
     dc, rtc, *_ = make_dispatcher(meta128, fuse_rope=True, context_length=4096)           # one sequence: compact shape
     m128 = dict(mapping(), rope_cos=0x7300_0000_0000, rope_sin=0x7300_1000_0000)
-    assert dc.compact and len(dc.build_launches(0, m128, 0x7200_0000_0000)[1][1]) == 29
+    assert dc.compact and len(dc.build_launches(0, m128, 0x7200_0000_0000)[1][1]) == 31
     assert rtc.loaded[1][1] == "vteb_split_kv_partial_compact_rope_d128_kernel"
+    # fused append: no append launch; the split launch carries the new rows; without rotation the type is -1
+    df, rtf, *_ = make_dispatcher(meta128, fuse_append=True, context_length=4096)
+    lf = df.build_launches(0, mapping(), 0x7200_0000_0000)
+    assert len(lf) == 2 and rtf.loaded[1][1] == "vteb_split_kv_partial_compact_rope_d128_kernel"
+    tail = [a.value for a in lf[0][1][-6:]]
+    assert tail[2:4] == [-1, 0] and tail[4:] == [mapping()['blk.0.k_proj.output'], mapping()['blk.0.v_proj.output']]
+    dfr, *_ = make_dispatcher(meta128, fuse_append=True, fuse_rope=True, context_length=4096)
+    tail = [a.value for a in dfr.build_launches(0, m128, 0x7200_0000_0000)[0][1][-6:]]
+    assert tail[:4] == [0x7300_0000_0000, 0x7300_1000_0000, 0, 128] and tail[4] == mapping()['blk.0.k_proj.output']
+    with pytest.raises(CudaSafetyError):
+        make_dispatcher(meta128, fuse_append=True, compat=True)
     with pytest.raises(CudaSafetyError):
         make_dispatcher(dict(meta, rotary_dim=48), fuse_rope=True)
     with pytest.raises(CudaSafetyError):

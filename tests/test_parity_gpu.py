@@ -274,6 +274,57 @@ def test_append_then_attend_in_one_graph(cuda_runtime, codegen):
         ex.cleanup()
 
 
+@pytest.mark.parametrize("shape", [(2, 12, 2, 128), (3, 32, 8, 64), (2, 8, 2, 256)], ids=["d128", "d64", "d256"])
+def test_append_fused_into_the_split_kernel(cuda_runtime, codegen, shape):
+    """No append launch: the split kernel's CTA whose tile holds a sequence's newest position writes
+    the new K and V rows into the cache and into its tile.  Outputs and cache contents must equal the
+    append-launch route bit for bit, over growing sequences that cross tile and split boundaries."""
+    B, Hq, Hkv, D = shape
+    cfg = DecodeConfig("append_fused", 23, B, Hq, Hkv, D, 200, 200, 2)
+    layers = [make_layer_inputs(cfg, l) for l in range(2)]
+    steps = [0, 1, 15, 16, 31, 32, 33, 63, 64, 127, 199]
+    rng = np.random.default_rng(4)
+    news = [[(rng.standard_normal((B, Hkv, D), dtype=np.float32).astype(np.float16),
+              rng.standard_normal((B, Hkv, D), dtype=np.float32).astype(np.float16)) for _ in range(2)] for _ in steps]
+    results = {}
+    for fused in (False, True):
+        for variant in ("full", "compact"):
+            ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), B, cfg.max_seq, 2, with_append=True,
+                                         fuse_append=fused, num_splits=3, min_chunk=0, variant=variant)
+            try:
+                for l, (q, k, v, _) in enumerate(layers):
+                    ex.upload_layer(l, q, k, v)
+                outs = []
+                for si, base in enumerate(steps):
+                    off = np.array([(base + 7 * b) % 200 for b in range(B)], dtype=np.int32)
+                    for l in range(2):
+                        ex.upload_new_kv(l, *news[si][l])
+                    outs.append(ex.execute_decode_batch(off))
+                rows = [ex.download_cache_rows(0, b, 200) for b in range(B)]
+                results[(fused, variant)] = (outs, rows)
+                assert ex.kernel_launches_per_step == (4 if fused else 6)
+            finally:
+                ex.cleanup()
+    # oracle for the whole sequence of steps
+    caches = [(k.copy(), v.copy()) for _, k, v, _ in layers]
+    for si, base in enumerate(steps):
+        off = np.array([(base + 7 * b) % 200 for b in range(B)], dtype=np.int32)
+        for l, (q, _, _, _) in enumerate(layers):
+            k, v = caches[l]
+            orc.kv_cache_append(news[si][l][0], news[si][l][1], k, v, off)
+            ref = orc.decode_attention(q, k, v, off)
+            for key in results:
+                assert_parity(results[key][0][si][l], ref, tight=5e-5)
+    for variant in ("full", "compact"):
+        a, b = results[(False, variant)], results[(True, variant)]
+        for oa, ob in zip(a[0], b[0]):
+            assert np.array_equal(oa, ob)
+        for (ka, va), (kb, vb) in zip(a[1], b[1]):
+            assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+        for bi in range(B):
+            assert np.array_equal(a[1][bi][0], caches[0][0][bi]) and np.array_equal(a[1][bi][1], caches[0][1][bi])
+
+
 def test_fp16_output_variant(cuda_runtime, codegen):
     cfg, lens = SMALL_CASES["group8_d128"]
     q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)

@@ -74,7 +74,7 @@ def test_rotation_modes_match_oracle_and_each_other(cuda_runtime, codegen, name)
 
     for splits, variant in ((1, "full"), (4, "full"), (3, "compact")):
         got = {mode: run_steps(cuda_runtime, codegen, cfg, meta, mode, layers, news, offsets_per_step, splits, variant)
-               for mode in ("separate", "fused")}
+               for mode in ("separate", "fused", "fused-append")}
         caches = [(k.copy(), v.copy()) for _, k, v, _ in layers]
         for step, off in enumerate(offsets_per_step):
             for l, (q, _, _, _) in enumerate(layers):
@@ -83,7 +83,7 @@ def test_rotation_modes_match_oracle_and_each_other(cuda_runtime, codegen, name)
                 k, v = caches[l]
                 orc.kv_cache_append(k_rot, v_new, k, v, off)
                 ref = orc.decode_attention(q_rot, k, v, off)
-                for mode in ("separate", "fused"):
+                for mode in ("separate", "fused", "fused-append"):
                     out, rows, q_after = got[mode][step]
                     max_abs, rel = orc.parity_metrics(out[l], ref)
                     assert max_abs <= MAX_ABS and rel <= REL_L2, (mode, step, l, max_abs, rel)
@@ -101,6 +101,8 @@ def test_rotation_modes_match_oracle_and_each_other(cuda_runtime, codegen, name)
                             assert np.array_equal(q_after, q)              # left as it was
             # the two routes round at the same points: identical output bits
             assert np.array_equal(got["separate"][step][0], got["fused"][step][0]), (splits, variant, step)
+            # ... and so does the route whose split kernel also does the append (no append launch)
+            assert np.array_equal(got["separate"][step][0], got["fused-append"][step][0]), (splits, variant, step)
 
 
 def test_rotation_kernel_handles_several_tokens_and_any_grid(cuda_runtime, codegen):

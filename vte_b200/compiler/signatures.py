@@ -32,12 +32,12 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_partial_d64_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_d128_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_d256_kernel": _FAST_PARTIAL,
-    "vteb_split_kv_partial_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL,
-    "vteb_split_kv_partial_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL,
-    "vteb_split_kv_partial_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL,
-    "vteb_split_kv_partial_compact_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL,
-    "vteb_split_kv_partial_compact_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL,
-    "vteb_split_kv_partial_compact_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL,
+    "vteb_split_kv_partial_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],     # + new K row, new V row (fused append)
+    "vteb_split_kv_partial_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],
+    "vteb_split_kv_partial_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],
+    "vteb_split_kv_partial_compact_rope_d64_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],
+    "vteb_split_kv_partial_compact_rope_d128_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],
+    "vteb_split_kv_partial_compact_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],
     "vteb_split_kv_partial_compact_d64_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_compact_d128_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_compact_d256_kernel": _FAST_PARTIAL,

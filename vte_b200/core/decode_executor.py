@@ -38,13 +38,14 @@ class DecodeAttentionExecutor:
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
                  emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
                  fused_combine: Optional[bool] = None, variant: str = "auto", rope: str = "off",
-                 rope_theta: float = 1e6, tensor_maps: bool = True):
+                 rope_theta: float = 1e6, tensor_maps: bool = True, fuse_append: bool = False):
         self.hip = hip
         # rope: "off" = Q and K arrive rotated; "separate" = the reference's standalone rotation
         # launch runs before the append (rotating the projections in place); "fused" = the append
         # rotates K and the split kernel rotates Q.  Either way the step includes the append.
-        if rope not in ("off", "separate", "fused"):
-            raise CudaSafetyError(f"rope must be off, separate or fused, not {rope!r}")
+        # "fused-append": as "fused", and the split kernel also does the append (no append launch).
+        if rope not in ("off", "separate", "fused", "fused-append"):
+            raise CudaSafetyError(f"rope must be off, separate, fused or fused-append, not {rope!r}")
         self.rope = rope
         if rope != "off":
             with_append = True
@@ -99,7 +100,8 @@ class DecodeAttentionExecutor:
             num_splits=num_splits, fixed_chunk_size=fixed_chunk_size, compat=compat, min_chunk=min_chunk,
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
             prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant,
-            fuse_rope=(rope == "fused"), tensor_maps=tensor_maps, work_ptr=self.out_all.ptr + self._out_tail)
+            fuse_rope=rope in ("fused", "fused-append"), fuse_append=(rope == "fused-append" or fuse_append), tensor_maps=tensor_maps,
+            work_ptr=self.out_all.ptr + self._out_tail)
 
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
         self.v_cache = [A(self.kv_bytes, f"kv_cache.v.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
@@ -183,7 +185,7 @@ class DecodeAttentionExecutor:
         n = 0
         for l in range(self.L):
             launches = self.dispatcher.build_launches(l, self.tensor_mapping, self.offsets.ptr, batch=self.B)
-            if not self.with_append:
+            if not self.with_append and not self.dispatcher.fuse_append:
                 launches = launches[1:]
             if self.launch_rewriter is not None:
                 launches = self.launch_rewriter(l, launches)
@@ -206,7 +208,7 @@ class DecodeAttentionExecutor:
             if not self.use_graph:
                 n = len(self.dispatcher.build_launches(0, self.tensor_mapping, self.offsets.ptr, batch=self.B))
                 n += 1 if self.rope == "separate" else 0
-                self.kernel_launches_per_step = (n if self.with_append else n - 1) * self.L
+                self.kernel_launches_per_step = (n if (self.with_append or self.dispatcher.fuse_append) else n - 1) * self.L
                 return
             self.hip.stream_begin_capture()
             try:

@@ -84,7 +84,7 @@ class SplitKVAttentionDispatcher:
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
                  strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True,
                  fused_combine: bool | None = None, variant: str = "auto", fuse_rope: bool = False,
-                 tensor_maps: bool = True, work_ptr: int | None = None):
+                 tensor_maps: bool = True, work_ptr: int | None = None, fuse_append: bool = False):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -169,9 +169,15 @@ class SplitKVAttentionDispatcher:
         # ['rope_sin'] (vte/core/kernel_arg_builder.py:394-395), type and width from the metadata keys
         # `rope_type` / `rotary_dim` (:401-406).  The reference tried this fusion and took it out again
         # (docs/PERFORMANCE.md, "RoPE fusion into Split-KV attention").
+        # fuse_append: no append launch at all; the split kernel's CTA whose tile holds a sequence's newest
+        # position writes the new K row (rotated when fuse_rope) and V row into the cache and into its
+        # tile.  A layer is then split + combine.  Uses the rotating kernels (rotation type -1 = none).
+        self.fuse_append = bool(fuse_append)
         self.fuse_rope = bool(fuse_rope)
         self.rope_type = int(self.metadata.get('rope_type', 0))
         self.rotary_dim = int(self.metadata.get('rotary_dim', self.head_dim))
+        if self.fuse_append and self.compat:
+            raise CudaSafetyError("fuse_append needs the fast kernels")
         if self.fuse_rope:
             if self.compat:
                 raise CudaSafetyError("fuse_rope needs the fast kernels")
@@ -241,7 +247,7 @@ class SplitKVAttentionDispatcher:
             else:
                 self._kernel_cache['partial'] = load(
                     'decode_attention',
-                    f"vteb_split_kv_partial_{'compact_' if self.compact else ''}{'rope_' if self.fuse_rope else ''}d{self.head_dim}_kernel")
+                    f"vteb_split_kv_partial_{'compact_' if self.compact else ''}{'rope_' if (self.fuse_rope or self.fuse_append) else ''}d{self.head_dim}_kernel")
                 # short split lists (batched decode): one warp per (sequence, head) row;
                 # long ones (one sequence spread over every SM): one CTA per 32 columns
                 self._rows_combine = self.max_chunks <= 64
@@ -371,6 +377,13 @@ class SplitKVAttentionDispatcher:
                 raise CudaSafetyError("fuse_rope: rope_cos / rope_sin missing from the tensor mapping or misaligned")
             rope_tail = [vp(cos_ptr), vp(sin_ptr), ci(self.rope_type), ci(self.rotary_dim)]
         append = (append_fn, append_args + rope_tail, (batch, Hkv, 1), (D, 1, 1), 0)
+        split_tail = list(rope_tail)
+        if self.fuse_rope or self.fuse_append:
+            if not self.fuse_rope:
+                split_tail = [vp(0), vp(0), ci(-1), ci(0)]                 # rotation type -1: none
+            if self.fuse_append and (not k_proj_ptr or not v_proj_ptr or k_proj_ptr % 4 or v_proj_ptr % 4):
+                raise CudaSafetyError("fuse_append: the new K / V rows could not be resolved or are misaligned")
+            split_tail += [vp(k_proj_ptr if self.fuse_append else 0), vp(v_proj_ptr if self.fuse_append else 0)]
 
         reference_partial_args = [
             vp(q_ptr), vp(k_cache_ptr), vp(v_cache_ptr),
@@ -410,18 +423,19 @@ class SplitKVAttentionDispatcher:
         partial_args = reference_partial_args + [
             ci(batch), ci(self.min_chunk), ci(flags), vp(0), vp(self._work.ptr), vp(self._work.ptr + 4),
             vp(next_k), vp(next_v),
-            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0), tmap_k, tmap_v] + rope_tail
+            vp(output_ptr if pass_output else 0), ci(out_kind if pass_output else 0), tmap_k, tmap_v] + split_tail
         partial = (partial_fn, partial_args, (n_ctas, 1, 1), (plan.threads, 1, 1), plan.smem_bytes)
+        head = [] if self.fuse_append else [append]
         if self.fused_combine or direct:
-            return [append, partial]
+            return head + [partial]
         if self._rows_combine:
             rows = batch * Hq
             epl = self.hip.combine_rows_epl(rows, D)
             units = rows * (D // (32 * epl))
             combine_args = reduce_args + [ci(out_kind), vp(self._work.ptr), ci(rows), ci(epl)]
-            return [append, partial, (reduce_fn, combine_args, ((units + 7) // 8, 1, 1), (256, 1, 1), 0)]
+            return head + [partial, (reduce_fn, combine_args, ((units + 7) // 8, 1, 1), (256, 1, 1), 0)]
         dsplit = plan.combine_dsplit
         combine_args = reduce_args + [ci(dsplit), vp(self._work.ptr)]
         combine_smem = min(C, 256) * 4
         combine = (reduce_fn, combine_args, (batch * Hq * dsplit, 1, 1), (256, 1, 1), combine_smem)
-        return [append, partial, combine]
+        return head + [partial, combine]

@@ -45,6 +45,9 @@ struct FastArgs {
     // tensor maps over the K and V caches (rows = positions of all sequences, 64-half boxes of
     // `tile` rows, 128-byte swizzle); used for whole tiles when kFlagTensorMaps is set
     const KvTensorMap* tmap_k; const KvTensorMap* tmap_v;
+    // fused append (rotating kernels only): this step's K and V projections [B, Hkv, D]; the CTA whose
+    // tile holds a sequence's newest position writes the row into the cache and into its tile
+    const __half* k_new; const __half* v_new;
 };
 
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
@@ -205,6 +208,28 @@ __device__ __forceinline__ ItemGeometry decode_item(const FastArgs& a, const Fas
     return g;
 }
 
+// Fused append: the newest row of a sequence for the item's head group (`new_row`, hg * D halves,
+// rotated at `pos` unless rope_type < 0 or `rotate` is false) goes to its place in the cache and to
+// row `r` of the tile at `tile_dst` (swizzled layout), four bytes per lane and step.
+template <int D>
+__device__ __forceinline__ void append_row_to_tile_and_cache(const __half* __restrict__ new_row, __half* __restrict__ cache_row,
+                                                             uint32_t tile_dst, int r, int hg, int blk_bytes, bool rotate,
+                                                             const __half* cos_table, const __half* sin_table, int pos,
+                                                             int rope_type, int rotary_dim, int lane) {
+    for (int idx = lane; idx < hg * D / 2; idx += 32) {
+        const int head = (2 * idx) / D, d = 2 * idx - head * D;
+        const __half* x = new_row + head * D;
+        const __half y0 = rotate ? rope_channel(x, d, D, cos_table, sin_table, pos, rope_type, rotary_dim) : x[d];
+        const __half y1 = rotate ? rope_channel(x, d + 1, D, cos_table, sin_table, pos, rope_type, rotary_dim) : x[d + 1];
+        const __half2 y = __halves2half2(y0, y1);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&y);
+        reinterpret_cast<uint32_t*>(cache_row)[idx] = w;
+        const int chunk = idx >> 2;                                  // 16-byte chunk of the row
+        const uint32_t addr = tile_dst + (chunk >> 3) * blk_bytes + r * 128 + ((((chunk & 7) ^ (r & 7))) << 4) + (idx & 3) * 4;
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(w) : "memory");
+    }
+}
+
 template <int D, int CW, bool kRope = false>
 __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 {
@@ -306,7 +331,25 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         (long long)pos0 * pos_stride;
                     const unsigned char* src_last = src + (long long)(g.end - 1 - pos0) * pos_stride;
                     const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes);
-                    if (use_tensor_maps && nvalid == plan.tile) {
+                    bool append_here = false;
+                    if constexpr (kRope) {
+                        append_here = a.k_new != nullptr && g.end == a.kv_offsets[g.b] + 1 && pos0 + nvalid >= g.end;
+                    }
+                    if (append_here) {
+                        // The tile ends with the sequence's newest position, whose row is not in the cache yet:
+                        // older rows come from the cache (masked rows are filled from the new row, which is
+                        // finite), then the new row is rotated and written to the cache and into the tile.
+                        const __half* knew = a.k_new + ((long long)g.b * a.num_kv_heads + (long long)g.hgroup * plan.hg) * D;
+                        copy_rows_async(src, reinterpret_cast<const unsigned char*>(knew), dst, nrows, nvalid - 1, plan.row_bytes,
+                                        plan.blk_bytes, pos_stride, lane);
+                        asm volatile("cp.async.wait_all;" ::: "memory");
+                        __syncwarp();
+                        __half* cache_row = const_cast<__half*>(a.k_cache) + (long long)g.b * a.kv_batch_stride +
+                                            (long long)(g.end - 1) * a.num_kv_heads * D + (long long)g.hgroup * plan.hg * D;
+                        append_row_to_tile_and_cache<D>(knew, cache_row, dst, nvalid - 1, plan.hg, plan.blk_bytes, true, a.rope_cos,
+                                                        a.rope_sin, g.end - 1, a.rope_type, a.rotary_dim, lane);
+                        mbar_arrive(bar);                       // every lane: releases its own stores
+                    } else if (use_tensor_maps && nvalid == plan.tile) {
                         // a whole tile: one elected lane issues one box per 128-byte column block
                         if (lane == 0) {
                             mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
@@ -368,7 +411,22 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     (long long)hd.pos0 * pos_stride;
                 const unsigned char* src_last = src + (long long)(hd.last_pos - hd.pos0) * pos_stride;
                 const uint32_t dst = smem_u32(stages + (size_t)stage * plan.stage_bytes) + plan.tile * plan.row_bytes;
-                if (use_tensor_maps && hd.nvalid == plan.tile) {
+                bool append_here = false;
+                if constexpr (kRope) {
+                    append_here = a.v_new != nullptr && hd.last_pos == a.kv_offsets[hd.b] && hd.pos0 + hd.nvalid > hd.last_pos;
+                }
+                if (append_here) {
+                    const __half* vnew = a.v_new + ((long long)hd.b * a.num_kv_heads + (long long)hd.hgroup * plan.hg) * D;
+                    copy_rows_async(src, reinterpret_cast<const unsigned char*>(vnew), dst, nrows, hd.nvalid - 1, plan.row_bytes,
+                                    plan.blk_bytes, pos_stride, lane);
+                    asm volatile("cp.async.wait_all;" ::: "memory");
+                    __syncwarp();
+                    __half* cache_row = const_cast<__half*>(a.v_cache) + (long long)hd.b * a.kv_batch_stride +
+                                        (long long)hd.last_pos * a.num_kv_heads * D + (long long)hd.hgroup * plan.hg * D;
+                    append_row_to_tile_and_cache<D>(vnew, cache_row, dst, hd.nvalid - 1, plan.hg, plan.blk_bytes, false, nullptr,
+                                                    nullptr, 0, -1, 0, lane);
+                    mbar_arrive(bar);
+                } else if (use_tensor_maps && hd.nvalid == plan.tile) {
                     if (lane == 0) {
                         mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
                         const int x0 = hd.hgroup * plan.hg * D, y = hd.b * rows_per_seq + hd.pos0;
@@ -772,6 +830,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
         a.output = output; a.out_kind = out_kind;                                                     \
         a.rope_cos = nullptr; a.rope_sin = nullptr; a.rope_type = 0; a.rotary_dim = 0;                \
+        a.k_new = nullptr; a.v_new = nullptr;                                                         \
         a.tmap_k = &tmap_k; a.tmap_v = &tmap_v;                                                       \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM, CWARPS>(a);                                                            \
@@ -792,7 +851,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         void* __restrict__ output, int out_kind, const __grid_constant__ KvTensorMap tmap_k,          \
         const __grid_constant__ KvTensorMap tmap_v,                                                   \
         const __half* __restrict__ cos_cache, const __half* __restrict__ sin_cache,                   \
-        int rope_type, int rotary_dim)                                                                \
+        int rope_type, int rotary_dim, const __half* __restrict__ k_new,                              \
+        const __half* __restrict__ v_new)                                                             \
     {                                                                                                 \
         FastArgs a;                                                                                   \
         a.q = q; a.k_cache = k_cache; a.v_cache = v_cache;                                            \
@@ -804,7 +864,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.next_k_cache = next_k_cache; a.next_v_cache = next_v_cache;                                 \
         a.output = output; a.out_kind = out_kind;                                                     \
         a.rope_cos = cos_cache; a.rope_sin = sin_cache; a.rope_type = rope_type;                      \
-        a.rotary_dim = rotary_dim;                                                                    \
+        a.rotary_dim = rotary_dim; a.k_new = k_new; a.v_new = v_new;                                  \
         a.tmap_k = &tmap_k; a.tmap_v = &tmap_v;                                                       \
         (void)head_dim;                                                                               \
         fast_partial_body<DIM, CWARPS, true>(a);                                                      \

@@ -331,6 +331,7 @@ __device__ __forceinline__ void rope_rotate_q_words(uint32_t (&q)[KS * 2], const
                                                     const __half* sin_table, int pos, int rope_type,
                                                     int rotary_dim, int t) {
     constexpr int D = KS * 16;
+    if (rope_type < 0) return;                                      // no rotation asked for
     if (rope_type == 1) {
         const __half* c = cos_table + (long long)pos * D;
         const __half* s = sin_table + (long long)pos * D;
@@ -358,6 +359,7 @@ __device__ __forceinline__ void rope_rotate_q_words(uint32_t (&q)[KS * 2], const
 __device__ __forceinline__ __half rope_channel(const __half* x, int d, int D, const __half* cos_table,
                                                const __half* sin_table, int pos, int rope_type, int rotary_dim) {
     float y1, y2;
+    if (rope_type < 0) return x[d];                                 // no rotation asked for
     if (rope_type == 1) {
         const int i = d >> 1;
         rope_pair(__half2float(x[2 * i]), __half2float(x[2 * i + 1]),
