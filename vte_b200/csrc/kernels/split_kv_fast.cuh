@@ -27,6 +27,10 @@
 // warps of a KV head exchange (m, l, o) through shared memory and the merged
 // state is stored to partial_m / partial_l / partial_o.
 //
+// The rotating variants (`..._rope_...`) rotate Q while loading it and, when handed this step's K
+// and V projections, also do the cache append: the loader warps of the CTA whose tile ends with a
+// sequence's newest position write that row into the cache and into the tile.
+//
 // Every wait is bounded; a wait that gives up stores a code in `*status`,
 // raises the CTA's abort word, and the CTA's warps return (the loader warps
 // first wait for their own outstanding copies).
