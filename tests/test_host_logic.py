@@ -454,5 +454,18 @@ def test_codegen_compiles_and_recompiles_once_on_load_failure(tmp_path):
     assert flaky.calls == 2 and Path(path).stat().st_mtime_ns > mtime
 
 
+def test_every_kernel_of_the_signature_table_is_in_the_cubin():
+    """The argument-count table and the cubin must not drift apart: every kernel the table lists has
+    a code section of that name in the ahead-of-time cubin, and every exported `vteb_*` /
+    reference-named kernel of the cubin is in the table."""
+    import re
+    from vte_b200.compiler.codegen import CodegenEngine
+    data = Path(CodegenEngine().compile_kernel("decode_attention", "sm_100a")).read_bytes()
+    for name in KERNEL_SIGNATURES:
+        assert b".text." + name.encode() + b"\0" in data, name
+    in_cubin = {m.decode() for m in re.findall(rb"\.text\.([A-Za-z0-9_]+_kernel)\0", data)}
+    assert in_cubin == set(KERNEL_SIGNATURES), in_cubin ^ set(KERNEL_SIGNATURES)
+
+
 def test_oom_error_is_a_safety_error():
     assert issubclass(MemoryGuardianOOMError, CudaSafetyError)
