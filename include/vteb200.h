@@ -150,10 +150,10 @@ typedef struct vteb_fast_plan {
     int combine_smem_bytes; /* per split, up to 256 splits: min(max_chunks, 256) * this */
 } vteb_fast_plan;
 int vteb_split_kv_plan(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
-/* Same for the compact CTA shape (4 consumer warps + 2 loader warps, still one CTA per
- * SM): it leaves register-file room beside it for the CTAs of the combine launch, which
- * shortens a layer whose whole split launch lasts only some microseconds.  `ok` is 0 when
- * a head group needs more than four consumer warps. */
+/* Same for the compact CTA shape (6 consumer warps + 2 loader warps of at most 160
+ * registers, still one CTA per SM): it leaves register-file room beside it for the CTAs of
+ * the combine launch, which shortens a layer whose whole split launch lasts only some
+ * microseconds.  `ok` is 0 when a head group needs more than six consumer warps. */
 int vteb_split_kv_plan_compact(int num_q_heads, int num_kv_heads, int head_dim, vteb_fast_plan* plan);
 /* Encodes the 128-byte tensor map the fast split kernels take for a K or V cache: the cache
  * seen as `n_rows` position rows (all sequences, one after another) of `row_halves` =
@@ -209,8 +209,11 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
  *     (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make
  *     that first call before any stream capture begins.
  *   - Every call uses the same array and finds the previous call's contents in
- *     it: the entry point clears the two words that must start at zero, and two
- *     calls that overlap on the GPU (different streams, no ordering) race.
+ *     it: the entry point clears the work-queue word, which must start at zero, and
+ *     two calls that overlap on the GPU (different streams, no ordering) race.
+ *   - The status word of the kernels' bounded waits lives in the array too and is
+ *     left alone by later calls: read (and clear) it with vteb_noalloc_check_status
+ *     after synchronising, as vteb_check_status does for caller-provided work words.
  *   - It calls no cudaMalloc, cudaFree or other allocating routine. */
 #define VTEB_NOALLOC_SCRATCH_BYTES (16u << 20)
 int vteb_split_kv_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
@@ -218,6 +221,13 @@ int vteb_split_kv_decode_noalloc(const void* q, const void* k_cache, const void*
                                  int batch, int num_q_heads, int num_kv_heads, int head_dim,
                                  float scale, long long kv_batch_stride, int max_chunks,
                                  int min_chunk, unsigned flags, int n_ctas, void* stream);
+
+/* vteb_check_status for the work words inside the library's own array: returns
+ * VTEB_ERR_DEVICE_STATUS (and clears the word) when a bounded wait of any
+ * vteb_split_kv_decode_noalloc call since the last check gave up, 0 otherwise, also
+ * when no such call has been made on this device yet.  Synchronises `stream`.  No
+ * counterpart in the reference. */
+int vteb_noalloc_check_status(void* stream);
 
 /* Writes the current token's K/V rows at position kv_offsets[b]
  * (kv_cache_append.hip.template:13-39; launch built at split_kv_attention.py:186-194). */

@@ -133,6 +133,7 @@ def _declare(lib):
         "vteb_split_kv_decode_noalloc": (i, [vp, vp, vp, vp, vp, i, i, i, i, i, f, ll, i, i, u, i, vp]),
         "vteb_kv_cache_append": (i, [vp, vp, vp, vp, vp, i, i, i, ll, vp]),
         "vteb_check_status": (i, [vp, vp]),
+        "vteb_noalloc_check_status": (i, [vp]),
         "vteb_fill_normal_f16": (i, [vp, sz, ull, f, f, f, vp]),
         "vteb_read_bandwidth_probe": (i, [vp, sz, vp, i, vp]),
     }
@@ -712,6 +713,14 @@ class CudaRuntime:
         if err == ERR_DEVICE_STATUS:
             raise CudaRuntimeError(self._last_error(), code=err)
         self._check_error(err, "vteb_check_status")
+
+    def noalloc_check_status(self) -> None:
+        """`check_status` for the work words inside the library's own scratch array: raises if a
+        bounded wait of any `split_kv_decode_noalloc` call since the last check gave up."""
+        err = self._lib.vteb_noalloc_check_status(self._stream)
+        if err == ERR_DEVICE_STATUS:
+            raise CudaRuntimeError(self._last_error(), code=err)
+        self._check_error(err, "vteb_noalloc_check_status")
 
     def fill_normal_f16(self, dst, n: int, seed: int, sigma: float = 1.0, outlier_prob: float = 0.0,
                         outlier_scale: float = 1.0) -> None:

@@ -33,6 +33,7 @@ TARGET_CHUNK_POSITIONS = 256      # smallest chunk length aimed at when many seq
 FLAG_WRITE_EMPTY_O = 1
 FLAG_DIRECT_OUTPUT = 2
 FLAG_TENSOR_MAPS = 4
+FLAG_PREFETCH_Q = 8
 COMPACT_MAX_CONTEXT = 262144      # one sequence up to this long: the compact CTA shape (launches of tens of microseconds)
 UNSPLIT_MAX_CONTEXT = 128         # below this, one CTA per (sequence, head group) finishes before a combine could launch
 
@@ -401,6 +402,7 @@ class SplitKVAttentionDispatcher:
         items = batch * plan.n_hgroups * C
         n_ctas = max(1, min(items, self.num_sms))
         flags = FLAG_WRITE_EMPTY_O if self.strict_empty_splits else 0
+        flags |= int(os.environ.get('VTEB_EXP_FLAGS', '0'))
         next_k = next_v = 0
         if self.prefetch_next_layer:
             next_k, next_v = self._resolve_kv_cache_ptrs(layer_idx + 1, {k: v for k, v in tensor_mapping.items()

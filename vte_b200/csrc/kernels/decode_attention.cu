@@ -462,11 +462,28 @@ __device__ __forceinline__ void fast_combine_kernel_body(
     int head_dim, int max_chunks, int dsplit, int* __restrict__ ticket)
 {
     extern __shared__ float combine_weight_sh[];   // [min(max_chunks, 256)]
+#ifdef VTEB_TRACE
+    // timeline trace (see split_kv_fast.cuh): first and last CTA stamp %globaltimer at entry, after the
+    // dependency wait and at the end, into [launch][2][4] 64-bit words at byte 256 + 64 * 3 * 10 * 16 * 8
+    unsigned long long* ctr = nullptr;
+    if (threadIdx.x == 0 && ticket != nullptr && (blockIdx.x == 0 || blockIdx.x + 1 == gridDim.x)) {
+        const int sel = blockIdx.x == 0 ? 0 : 1;
+        const int launch = atomicAdd(ticket + 1 + 18 + sel, 1);
+        if (launch < 64) ctr = reinterpret_cast<unsigned long long*>(ticket) + 32 + 64 * 3 * 10 * 16 + (launch * 2 + sel) * 4;
+        if (ctr) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ctr[0]));
+    }
+#endif
     grid_launch_dependents();
     grid_dependency_wait();
+#ifdef VTEB_TRACE
+    if (ctr) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ctr[1]));
+#endif
     if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
     combine_slice<false>(partial_m, partial_l, partial_o, output, out_kind, head_dim, max_chunks, dsplit,
                          blockIdx.x, combine_weight_sh);
+#ifdef VTEB_TRACE
+    if (ctr) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ctr[2]));
+#endif
 }
 
 extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_f16_kernel(
@@ -730,7 +747,7 @@ extern "C" __global__ void vteb_merge_shard_states_p2p_kernel(
         for (int r = 0; r < world && ok; ++r) {
             const volatile int* flag = flags + slot0 + r;
             while (*flag != step + 1) {
-                if (clock64() - t0 > 4000000000ll) { ok = 0; break; }   // ~2 s: give up, report, return
+                if (clock64() - t0 > kWaitLimitCycles) { ok = 0; break; }   // give up, report, return
             }
         }
         __threadfence_system();
@@ -836,7 +853,7 @@ extern "C" __global__ void __maxnreg__(80) vteb_split_kv_combine_push_kernel(
             }
         }
         if (all) break;
-        if (clock64() - t0 > 4000000000ll) { ok = false; break; }          // ~2 s: give up, report, return
+        if (clock64() - t0 > kWaitLimitCycles) { ok = false; break; }          // give up, report, return
     }
     if (!ok) { atomicCAS(status, 0, kStatusGridTimeout); return; }
     float M = kNeutralM;
@@ -884,7 +901,7 @@ extern "C" __global__ void vteb_merge_shard_states_ll_kernel(
             }
         }
         if (all) break;
-        if (clock64() - t0 > 4000000000ll) { ok = false; break; }          // ~2 s: give up, report, return
+        if (clock64() - t0 > kWaitLimitCycles) { ok = false; break; }          // give up, report, return
     }
     if (!ok) { atomicCAS(status, 0, kStatusGridTimeout); return; }
     if (d >= head_dim) return;

@@ -36,6 +36,10 @@
 // first wait for their own outstanding copies).
 #pragma once
 
+#ifndef VTEB_PIPELINE_BLOCKS
+#define VTEB_PIPELINE_BLOCKS 1   // 1: two 16-position blocks in flight per consumer warp; 0: one
+#endif
+
 struct FastArgs {
     const __half* q; const __half* k_cache; const __half* v_cache;
     float* partial_m; float* partial_l; float* partial_o;
@@ -57,6 +61,28 @@ struct FastArgs {
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
 constexpr int kFlagDirectOutput = 2;  // max_chunks == 1: normalise and store the attention output here, no partials
 constexpr int kFlagTensorMaps = 4;    // tmap_k / tmap_v are valid: whole tiles are fetched with tensor-map copies
+constexpr int kFlagPrefetchQ = 8;     // ask L2 for the first item's Q rows before the dependency wait (a hint: no data is read)
+
+// ---- optional timeline trace (compiled in with -DVTEB_TRACE=1, used by vte_b200/trace_timeline.py) ----
+// The status word's allocation is then a trace buffer: 64-bit words from byte 256 on,
+// [launch 0..63][traced CTA 0..2][warp 0..9][16 stamps]; per-CTA launch counters sit at byte 64.
+// Lane 0 of every warp of three CTAs (first, middle, last but two) stamps the SM cycle counter at fixed
+// points, plus %globaltimer at entry and exit so that CTAs and launches can be laid on one axis.
+#ifdef VTEB_TRACE
+struct TraceCtx { unsigned long long* base; };
+__device__ __forceinline__ unsigned long long trace_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define VTEB_TR(ctx, slot) do { if ((ctx).base != nullptr && (threadIdx.x & 31) == 0) (ctx).base[slot] = (unsigned long long)clock64(); } while (0)
+#define VTEB_TR_GT(ctx, slot) do { if ((ctx).base != nullptr && (threadIdx.x & 31) == 0) (ctx).base[slot] = trace_globaltimer(); } while (0)
+#define VTEB_TR_ADD(ctx, slot, v) do { if ((ctx).base != nullptr && (threadIdx.x & 31) == 0) (ctx).base[slot] += (unsigned long long)(v); } while (0)
+#else
+#define VTEB_TR(ctx, slot) do { } while (0)
+#define VTEB_TR_GT(ctx, slot) do { } while (0)
+#define VTEB_TR_ADD(ctx, slot, v) do { } while (0)
+#endif
 
 // Stores four (or two) normalised output values; out_kind 1 = fp16, 2 = fp32.
 __device__ __forceinline__ void store_out4(void* output, int out_kind, long long idx, float4 v) {
@@ -172,7 +198,7 @@ __device__ __forceinline__ void prefetch_range_l2(const unsigned char* base, lon
 
 // Grid-wide barrier for a grid whose CTAs are all resident (grid <= SM count, one CTA
 // per SM).  words[0] counts arrivals and is cleared by the last arriver, words[1] is a
-// generation number; one thread per CTA calls this.  The wait is bounded (~2 s).
+// generation number; one thread per CTA calls this.  The wait is bounded (kWaitLimitCycles).
 __device__ __forceinline__ bool grid_barrier_bounded(int* words, int n_ctas) {
     volatile int* gen = words + 1;
     const int my_gen = *gen;
@@ -186,7 +212,7 @@ __device__ __forceinline__ bool grid_barrier_bounded(int* words, int n_ctas) {
     }
     const long long t0 = clock64();
     while (*gen == my_gen) {
-        if (clock64() - t0 > 4000000000ll) return false;
+        if (clock64() - t0 > kWaitLimitCycles) return false;
     }
     __threadfence();
     return true;
@@ -278,6 +304,20 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+#ifdef VTEB_TRACE
+    TraceCtx tr; tr.base = nullptr;
+    {
+        __shared__ int trace_launch;
+        const int sel = (blockIdx.x == 0) ? 0 : (blockIdx.x == gridDim.x / 2) ? 1 : (blockIdx.x + 3 == gridDim.x) ? 2 : -1;
+        if (threadIdx.x == 0 && sel >= 0) trace_launch = atomicAdd(a.status + 15 + sel, 1);
+        __syncthreads();
+        if (sel >= 0 && trace_launch < 64)
+            tr.base = reinterpret_cast<unsigned long long*>(a.status - 1) + 32 +
+                      (((size_t)trace_launch * 3 + sel) * 10 + (threadIdx.x >> 5)) * 16;
+    }
+    VTEB_TR_GT(tr, 0);
+    VTEB_TR(tr, 1);
+#endif
     __syncthreads();
     grid_launch_dependents();
 
@@ -288,6 +328,14 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // ===================================================================== K loader
     if (warp == kLoaderWarpK) {
+        if ((a.flags & kFlagPrefetchQ) && lane == 0 && (int)blockIdx.x < total_items) {
+            // Q of the first item is read right after the dependency wait; when it is not in L2 by then
+            // (nothing produced it recently) the consumers start a DRAM latency late.  A prefetch moves no
+            // data into the SM, so it may run ahead of the kernel that writes Q: L2 is where that write lands.
+            const __half* q0 = a.q + ((long long)first_geom.b * a.num_q_heads + (long long)first_geom.hgroup * plan.hg * group) * D;
+            const unsigned qbytes = (unsigned)(plan.hg * group * D * 2);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(q0), "r"(qbytes) : "memory");
+        }
         int stage = 0, filled = 0;
         uint32_t empty_parity = 0;
         bool dep_done = false;
@@ -371,6 +419,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     mbar_arrive(bar);      // no copies belong to this tile
                 }
                 ++filled;
+                if (filled == 1) VTEB_TR(tr, 2);
+                if (filled == nstages) VTEB_TR(tr, 3);
+                if (!stop) VTEB_TR(tr, 4);
                 stage = (stage + 1 == nstages) ? 0 : stage + 1;
             }
             if (stop || !alive) break;
@@ -390,7 +441,10 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                   (long long)(g.end - g.start) * pos_stride, lane);
         }
         if (!dep_done) grid_dependency_wait();
+        VTEB_TR(tr, 5);
         asm volatile("cp.async.wait_all;" ::: "memory");   // own copies have landed before the warp leaves
+        VTEB_TR(tr, 8);
+        VTEB_TR_GT(tr, 9);
         return;
     }
 
@@ -521,15 +575,140 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                 (hh * (D / 64) + dhalf * (DW / 64)) * blk_bytes + plan.tile * plan.row_bytes;
     const uint32_t v_lane_x = (((lane >> 4) ^ (lane & 7)) << 4);
 
+    // ---- S = Q K^T of one 16-position block: sn[0] positions 0..7, sn[1] positions 8..15 (raw dot
+    // products, unscaled); two accumulation chains each; K fragments are fetched KC k-steps at a time
+    auto qk_block = [&](uint32_t kaddr, float (&sn)[2][2]) {
+        float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, s_alt[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        constexpr int KC = KS < 8 ? KS : 8;
+#pragma unroll
+        for (int kc = 0; kc < KS; kc += KC) {
+            uint32_t kf[KC][4];
+#pragma unroll
+            for (int i = 0; i < KC; ++i)
+                ldmatrix_x4((kaddr ^ (((kc + i) & 3) << 5)) + ((kc + i) >> 2) * blk_bytes, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
+#pragma unroll
+            for (int i = 0; i < KC; i += 2) {
+                const int ks = kc + i;
+                const uint32_t qa0 = q_frag[(2 * ks) * 32], qa1 = q_frag[(2 * ks + 1) * 32];
+                const uint32_t qb0 = q_frag[(2 * ks + 2) * 32], qb1 = q_frag[(2 * ks + 3) * 32];
+                mma_rows0to7(s[0][0], s[0][1], qa0, qa1, kf[i][0], kf[i][1]);
+                mma_rows0to7(s[1][0], s[1][1], qa0, qa1, kf[i][2], kf[i][3]);
+                mma_rows0to7(s_alt[0][0], s_alt[0][1], qb0, qb1, kf[i + 1][0], kf[i + 1][1]);
+                mma_rows0to7(s_alt[1][0], s_alt[1][1], qb0, qb1, kf[i + 1][2], kf[i + 1][3]);
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) { sn[n][0] = s[n][0] + s_alt[n][0]; sn[n][1] = s[n][1] + s_alt[n][1]; }
+    };
+
+    // ---- online softmax (log2 domain) of a block's raw scores and O += P V; `left` = positions of
+    // the block that belong to the item (may exceed 16), the rest are masked
+    auto softmax_pv = [&](const float (&sraw)[2][2], uint32_t vaddr, int left) {
+        // V fragments do not depend on the softmax: fetch the first 64 columns now
+        constexpr int VC = 4;                 // ldmatrix.x4.trans per chunk = 64 output columns
+        constexpr int NVC = NT / (2 * VC);    // chunks
+        uint32_t vf[2][VC][4];
+#pragma unroll
+        for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr ^ (i << 5), vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
+        float s[2][2];
+        float mx = kNeutralM;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const bool valid = (n * 8 + 2 * t + j) < left;
+                s[n][j] = valid ? sraw[n][j] * scale2 : kNeutralM;
+                mx = fmaxf(mx, s[n][j]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = fast_exp2(m_run - m_new);
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+            l_run *= corr;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) { o_acc[n][0] *= corr; o_acc[n][1] *= corr; }
+        }
+        m_run = m_new;
+        float p[2][2];
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const bool valid = (n * 8 + 2 * t + j) < left;
+                p[n][j] = valid ? fast_exp2(s[n][j] - m_new) : 0.f;
+            }
+        l_run += (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+        // P = P_hi + P_lo, both fp16: keeps ~22 bits of each probability.
+        uint32_t ph[2], pl[2];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const __half2 hi = __floats2half2_rn(p[n][0], p[n][1]);
+            const float2 hif = __half22float2(hi);
+            ph[n] = *reinterpret_cast<const uint32_t*>(&hi);
+            pl[n] = pack_half2(p[n][0] - hif.x, p[n][1] - hif.y);
+        }
+        // O += P V, 64 columns per chunk; the next chunk's fragments load meanwhile
+#pragma unroll
+        for (int ch = 0; ch < NVC; ++ch) {
+            if (ch + 1 < NVC) {
+#pragma unroll
+                for (int i = 0; i < VC; ++i)
+                    ldmatrix_x4_trans((vaddr ^ (i << 5)) + (ch + 1) * blk_bytes, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
+                                      vf[(ch + 1) & 1][i][2], vf[(ch + 1) & 1][i][3]);
+            }
+#pragma unroll
+            for (int i = 0; i < VC; ++i) {
+                const int n = 2 * (ch * VC + i);
+                float e0, e1, f0, f1;
+                mma_hi_lo(o_acc[n][0], o_acc[n][1], e0, e1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
+                mma_hi_lo(o_acc[n + 1][0], o_acc[n + 1][1], f0, f1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
+                // rows 8..15 of A carried P_lo; their product belongs to this thread's row too
+                o_acc[n][0] += e0; o_acc[n][1] += e1; o_acc[n + 1][0] += f0; o_acc[n + 1][1] += f1;
+            }
+        }
+    };
+
+    // Two blocks are in flight per warp: the scores of block i+1 are issued before the softmax and
+    // the P V product of block i, so the tensor pipe works on one block while the other goes through
+    // the shuffle / exp chain.  `pend_*` describe the block whose scores are known and whose softmax
+    // and P V are still to come; the stage that holds it is handed back only after its V rows were read.
+    float pend_s[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    uint32_t pend_vaddr = 0;
+    int pend_left = 0;
+    bool pending = false;
+    int held_stage = -1;                  // stage whose release waits for the pending block (-1: none)
+    auto finish_pending = [&]() {
+        softmax_pv(pend_s, pend_vaddr, pend_left);
+        pending = false;
+        if (held_stage >= 0) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * held_stage);
+            held_stage = -1;
+        }
+    };
+
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
     grid_dependency_wait();
+    VTEB_TR(tr, 2);
     if ((int)blockIdx.x < total_items) load_q(first_geom.b, first_geom.hgroup);
+    VTEB_TR(tr, 3);
+#ifdef VTEB_TRACE
+    bool trace_first_full = true;
+#endif
 
     for (;;) {
+#ifdef VTEB_TRACE
+        const long long trace_w0 = clock64();
+#endif
         if (!mbar_wait_bounded(full0 + 8 * stage, (full_parity >> stage) & 1u, abort_word)) {
             raise_abort(abort_word, a.status, kStatusFullTimeout);
             return;
         }
+#ifdef VTEB_TRACE
+        VTEB_TR_ADD(tr, 11, clock64() - trace_w0);
+        if (trace_first_full) { VTEB_TR(tr, 4); trace_first_full = false; }
+#endif
         full_parity ^= (1u << stage);
         const TileHeader* hd = headers + stage;
         const int flags = hd->flags;
@@ -540,6 +719,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         const int nvalid = hd->nvalid, blk0 = hd->blk0;
 
         if (flags & kTileFirst) {
+            // (no block is pending here: an item's last tile finishes it)
             m_run = kNeutralM; l_run = 0.f;
 #pragma unroll
             for (int n = 0; n < NT; ++n) { o_acc[n][0] = 0.f; o_acc[n][1] = 0.f; }
@@ -549,101 +729,37 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
         const uint32_t tile_base = smem_u32(stages + (size_t)stage * plan.stage_bytes);
         if (flags & kTileFirst) next_blk = sub;
+        bool pend_here = false;               // the pending block lies in this tile
         for (; next_blk < blk0 + blocks_per_tile; next_blk += plan.wph) {
             const int r0 = (next_blk - blk0) * kBlockPos;
             if (r0 >= nvalid) break;
-            // ---- S = Q K^T: s[0] positions 0..7, s[1] positions 8..15; two accumulation
-            // chains each; K fragments are fetched eight k-steps at a time
-            const uint32_t kaddr = (tile_base + r0 * 128 + k_lane_off) | k_lane_x;
-            float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, s_alt[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-            constexpr int KC = KS < 8 ? KS : 8;
+            float sn[2][2];
+            qk_block((tile_base + r0 * 128 + k_lane_off) | k_lane_x, sn);
+#if !VTEB_PIPELINE_BLOCKS
+            softmax_pv(sn, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, nvalid - r0);
+            continue;
+#endif
+            if (pending) finish_pending();
 #pragma unroll
-            for (int kc = 0; kc < KS; kc += KC) {
-                uint32_t kf[KC][4];
-#pragma unroll
-                for (int i = 0; i < KC; ++i)
-                    ldmatrix_x4((kaddr ^ (((kc + i) & 3) << 5)) + ((kc + i) >> 2) * blk_bytes, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
-#pragma unroll
-                for (int i = 0; i < KC; i += 2) {
-                    const int ks = kc + i;
-                    const uint32_t qa0 = q_frag[(2 * ks) * 32], qa1 = q_frag[(2 * ks + 1) * 32];
-                    const uint32_t qb0 = q_frag[(2 * ks + 2) * 32], qb1 = q_frag[(2 * ks + 3) * 32];
-                    mma_rows0to7(s[0][0], s[0][1], qa0, qa1, kf[i][0], kf[i][1]);
-                    mma_rows0to7(s[1][0], s[1][1], qa0, qa1, kf[i][2], kf[i][3]);
-                    mma_rows0to7(s_alt[0][0], s_alt[0][1], qb0, qb1, kf[i + 1][0], kf[i + 1][1]);
-                    mma_rows0to7(s_alt[1][0], s_alt[1][1], qb0, qb1, kf[i + 1][2], kf[i + 1][3]);
-                }
-            }
-            // ---- V fragments do not depend on the softmax: fetch the first 64 columns now
-            const uint32_t vaddr = (tile_base + r0 * 128 + v_lane_off) | v_lane_x;
-            constexpr int VC = 4;                 // ldmatrix.x4.trans per chunk = 64 output columns
-            constexpr int NVC = NT / (2 * VC);    // chunks
-            uint32_t vf[2][VC][4];
-#pragma unroll
-            for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr ^ (i << 5), vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
-            // ---- online softmax (log2 domain); positions past the item's end are masked
-            const int left = nvalid - r0;         // valid positions in this block (may exceed 16)
-            float mx = kNeutralM;
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const bool valid = (n * 8 + 2 * t + j) < left;
-                    s[n][j] = valid ? (s[n][j] + s_alt[n][j]) * scale2 : kNeutralM;
-                    mx = fmaxf(mx, s[n][j]);
-                }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run, mx);
-            const float corr = fast_exp2(m_run - m_new);
-            if (__any_sync(0xffffffffu, corr != 1.f)) {
-                l_run *= corr;
-#pragma unroll
-                for (int n = 0; n < NT; ++n) { o_acc[n][0] *= corr; o_acc[n][1] *= corr; }
-            }
-            m_run = m_new;
-            float p[2][2];
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const bool valid = (n * 8 + 2 * t + j) < left;
-                    p[n][j] = valid ? fast_exp2(s[n][j] - m_new) : 0.f;
-                }
-            l_run += (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
-            // P = P_hi + P_lo, both fp16: keeps ~22 bits of each probability.
-            uint32_t ph[2], pl[2];
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const __half2 hi = __floats2half2_rn(p[n][0], p[n][1]);
-                const float2 hif = __half22float2(hi);
-                ph[n] = *reinterpret_cast<const uint32_t*>(&hi);
-                pl[n] = pack_half2(p[n][0] - hif.x, p[n][1] - hif.y);
-            }
-            // ---- O += P V, 64 columns per chunk; the next chunk's fragments load meanwhile
-#pragma unroll
-            for (int ch = 0; ch < NVC; ++ch) {
-                if (ch + 1 < NVC) {
-#pragma unroll
-                    for (int i = 0; i < VC; ++i)
-                        ldmatrix_x4_trans((vaddr ^ (i << 5)) + (ch + 1) * blk_bytes, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
-                                          vf[(ch + 1) & 1][i][2], vf[(ch + 1) & 1][i][3]);
-                }
-#pragma unroll
-                for (int i = 0; i < VC; ++i) {
-                    const int n = 2 * (ch * VC + i);
-                    float e0, e1, f0, f1;
-                    mma_hi_lo(o_acc[n][0], o_acc[n][1], e0, e1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
-                    mma_hi_lo(o_acc[n + 1][0], o_acc[n + 1][1], f0, f1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
-                    // rows 8..15 of A carried P_lo; their product belongs to this thread's row too
-                    o_acc[n][0] += e0; o_acc[n][1] += e1; o_acc[n + 1][0] += f0; o_acc[n + 1][1] += f1;
-                }
-            }
+            for (int n = 0; n < 2; ++n) { pend_s[n][0] = sn[n][0]; pend_s[n][1] = sn[n][1]; }
+            pend_vaddr = (tile_base + r0 * 128 + v_lane_off) | v_lane_x;
+            pend_left = nvalid - r0;
+            pending = true;
+            pend_here = true;
+        }
+        if (flags & kTileLast) {
+            if (pending) finish_pending();
+            pend_here = false;
+            VTEB_TR(tr, 5);
         }
 
-        // Hand the stage back to the loader.
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+        // Hand the stage back to the loader, unless the pending block still needs its V rows.
+        if (pend_here) {
+            held_stage = stage;
+        } else {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+        }
 
         if (flags & kTileLast) {
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
@@ -705,6 +821,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 return;
             }
             merge_parity ^= 1u;
+            VTEB_TR(tr, 6);
 
             // One (KV head, query row) pair per warp pass: all lanes derive the pair's
             // weights from broadcast reads, then each lane merges its float4 columns.
@@ -774,11 +891,14 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             __syncwarp();
             if (lane == 0) mbar_arrive(merge_bar0 + 8);
             merge_pending = true;
+            VTEB_TR(tr, 7);
         } else {
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
         }
     }
 
+    VTEB_TR(tr, 8);
+    VTEB_TR_GT(tr, 9);
     if (kCompact || a.out_kind == 0 || (a.flags & kFlagDirectOutput)) return;
     // ===================================================================== in-launch combine
     // (needs all eight consumer warps; the host only asks for it then)

@@ -34,6 +34,14 @@ constexpr float kNeutralM = -1e30f;                      // reference's "empty s
 #endif
 constexpr int kSmemBudget = VTEB_SMEM_BUDGET_KB * 1024;  // dynamic shared memory the split kernel may use
 
+// Every device-side wait gives up after this many SM clock cycles (about two seconds at 2 GHz),
+// records a status code and returns.  A build with a smaller value (-DVTEB_WAIT_LIMIT_CYCLES=n)
+// lets a test watch a wait run out without anything hanging.
+#ifndef VTEB_WAIT_LIMIT_CYCLES
+#define VTEB_WAIT_LIMIT_CYCLES 4000000000
+#endif
+constexpr long long kWaitLimitCycles = VTEB_WAIT_LIMIT_CYCLES;
+
 // Status word written by a kernel that gave up on a wait.  The host reads it
 // after synchronising; zero means every wait completed.
 constexpr int kStatusOk = 0;
@@ -176,12 +184,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Waits for a barrier phase for at most `limit_cycles` SM clock cycles
-// (4e9 is about two seconds), also giving up as soon as another warp of the
+// (the default is about two seconds), also giving up as soon as another warp of the
 // CTA has raised `*abort_word` (pass nullptr to ignore it).  Returns false when
 // it gave up; the caller then records a status code and leaves.  The SM-local
 // cycle counter is used because reading %globaltimer costs microseconds.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word,
-                                                  long long limit_cycles = 4000000000ll) {
+                                                  long long limit_cycles = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t spin = 1; spin < (1u << 30); ++spin) {
@@ -195,11 +203,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // 16 bytes global -> shared through the asynchronous copy path (L2 only, no
-// register staging).  Measured on B200: one warp issuing these sustains
-// ~6.4 TB/s across 148 SMs, while cp.async.bulk requests of one 512-byte cache
-// row each are limited by the per-request rate of the bulk-copy engine
-// (~2.3 TB/s at 512 B, full rate only from 2 KB per request), and the padded
-// row layout that keeps ldmatrix conflict-free rules out larger bulk requests.
+// register staging); the source must be 16-byte aligned.  Used for ragged tiles
+// (the end of a split) and for caches a tensor map cannot describe; whole tiles
+// travel as tensor-map boxes (tma_load_box_2d), which cost the loader a handful
+// of instructions per tile instead of ~1,200 cycles.
 __device__ __forceinline__ void async_copy_16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }

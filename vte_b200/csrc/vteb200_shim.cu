@@ -650,7 +650,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
 
     bool compact = (flags & VTEB_ATTN_COMPACT) != 0;
     vteb::FastPlan p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, compact ? 1 : 0);
-    if (compact && !p.ok) {   // more KV heads per group than four consumer warps can serve
+    if (compact && !p.ok) {   // more KV heads per group than the compact shape's consumer warps can serve
         compact = false;
         p = vteb::make_fast_plan(num_q_heads, num_kv_heads, head_dim, 0);
     }
@@ -761,8 +761,9 @@ int vteb_split_kv_decode_noalloc(const void* q, const void* k_cache, const void*
     float* pm = reinterpret_cast<float*>(base + 256);
     float* pl = reinterpret_cast<float*>(base + 256 + stats);
     float* po = reinterpret_cast<float*>(base + 256 + 2 * stats);
-    // the work-queue ticket and the status word must start at zero
-    int rc = check_rt(cudaMemsetAsync(work, 0, 16, (cudaStream_t)stream), "scratch clear");
+    // the work-queue ticket must start at zero; the status word next to it keeps what an earlier
+    // call may have recorded until vteb_noalloc_check_status reads it
+    int rc = check_rt(cudaMemsetAsync(work, 0, 4, (cudaStream_t)stream), "scratch clear");
     if (rc) return rc;
     return vteb_split_kv_decode(q, k_cache, v_cache, kv_offsets, output, out_is_f32, pm, pl, po, work, batch,
                                 num_q_heads, num_kv_heads, head_dim, scale, kv_batch_stride, max_chunks, min_chunk,
@@ -792,11 +793,19 @@ int vteb_check_status(int* work, void* stream) {
     if ((rc = check_rt(cudaStreamSynchronize((cudaStream_t)stream), "status sync"))) return rc;
     if (status != 0) {
         cudaMemsetAsync(work + 1, 0, sizeof(int), (cudaStream_t)stream);
-        return fail(VTEB_ERR_DEVICE_STATUS, "split kernel gave up on a bounded wait (code %d: %s)", status,
+        return fail(VTEB_ERR_DEVICE_STATUS, "a kernel gave up on a bounded wait (code %d: %s)", status,
                     status == 1 ? "a tile never arrived" : status == 2 ? "a stage was never released"
-                                                                        : "the merge barrier never completed");
+                    : status == 3 ? "the merge barrier never completed"
+                                  : "another CTA or another rank never arrived");
     }
     return 0;
+}
+
+int vteb_noalloc_check_status(void* stream) {
+    REQUIRE_INIT();
+    if (g_device < 0 || g_device >= 64) return fail(VTEB_ERR_UNSUPPORTED, "device index %d not supported", g_device);
+    if (g_noalloc_ptr[g_device] == nullptr) return 0;     // no call has used the array on this device yet
+    return vteb_check_status(reinterpret_cast<int*>(g_noalloc_ptr[g_device]), stream);
 }
 
 int vteb_fill_normal_f16(void* dst, size_t n, unsigned long long seed, float sigma, float outlier_prob,
