@@ -273,10 +273,17 @@ def measure_sequences(args, rt, rdzv, rank, world, workload, n_layers, n_kv, ste
     if cfg.batch % world:
         return {"skipped": f"batch {cfg.batch} does not divide over {world} ranks"}
     mine = balanced_assignment(lengths, world)[rank] if world > 1 else np.arange(cfg.batch)
+    emulated = None
+    if world == 1 and getattr(args, "emulate_world", 0) > 1:
+        # one rank's share of an N-rank run, alone on this GPU (the sequences partition exchanges nothing,
+        # so this is what that rank would take): for tuning without N GPUs
+        emulated = (args.emulate_rank, args.emulate_world)
+        mine = balanced_assignment(lengths, args.emulate_world)[args.emulate_rank]
     my_lengths = lengths[mine]
     local = replace(cfg, batch=len(mine))
     ex = DecodeAttentionExecutor(rt, CodegenEngine(), metadata(cfg), local.batch, cfg.max_seq, n_layers,
-                                 n_kv_buffers=n_kv, output_f32=True, variant=args.variant)
+                                 n_kv_buffers=n_kv, output_f32=True, variant=args.variant,
+                                 num_splits=args.splits or None, min_chunk=None if args.min_chunk < 0 else args.min_chunk)
     try:
         for buf in range(n_kv):
             _fill_sequences(rt, ex, cfg, buf, mine)
@@ -297,7 +304,7 @@ def measure_sequences(args, rt, rdzv, rank, world, workload, n_layers, n_kv, ste
             ex.launch_step()
         t = timed_trials(rt, rdzv, ex.launch_step, steps)
         ex.dispatcher_check()
-        bytes_all = algorithmic_bytes(cfg, lengths) * n_layers
+        bytes_all = algorithmic_bytes(cfg, lengths if emulated is None else my_lengths) * n_layers
         step_s = t["median_ms"] / 1e3
         load = rdzv.allgather(str(int(my_lengths.astype(np.int64).sum())).encode())
         loads = [int(x) for x in load]
@@ -305,12 +312,14 @@ def measure_sequences(args, rt, rdzv, rank, world, workload, n_layers, n_kv, ste
             "workload": f"{workload}: batch {cfg.batch} x {cfg.num_q_heads} query / {cfg.num_kv_heads} KV heads of {cfg.head_dim}, "
                         f"context {int(lengths.min())}..{int(lengths.max())}, {n_layers} layers per step cycling {n_kv} distinct KV caches",
             "partition": (f"{local.batch} sequences per GPU, dealt longest-first onto the least loaded GPU; no collective"
-                          if world > 1 else "single GPU"),
+                          if world > 1 else "single GPU" if emulated is None else
+                          f"rank {emulated[0]} of {emulated[1]}'s share alone on one GPU (value = this share's bytes / time)"),
             "n_gpus": world, "scaling": "strong", "value": bytes_all / step_s / 1e12, "unit": UNIT,
             "us_per_layer_step": step_s * 1e6 / n_layers, "ms_per_step": t["median_ms"],
             "ms_per_step_min_max": [t["min_ms"], t["max_ms"]], "replays_per_trial": t["replays_per_trial"],
             "positions_per_gpu_max_over_mean": max(loads) / (sum(loads) / len(loads)),
-            "splits": ex.dispatcher.max_chunks, "kernels": "fast, compact CTAs" if ex.dispatcher.compact else "fast, full CTAs",
+            "splits": ex.dispatcher.max_chunks, "min_chunk": ex.dispatcher.min_chunk,
+            "kernels": "fast, compact CTAs" if ex.dispatcher.compact else "fast, full CTAs",
             "parity": {"against": "CPU oracle, layer 0, longest and shortest sequence of every rank", "max_abs": max_abs,
                        "rel_l2": rel, "within_tolerance": bool(max_abs <= 2e-3 and rel <= 1e-2)},
         }
@@ -476,7 +485,7 @@ def run_ours(args, rank, world, local_rank):
     rt = CudaRuntime(device_index=local_rank)
     rt.initialize()
     partition = args.partition or "replicas"
-    if world == 1:
+    if world == 1 and not (partition == "sequences" and args.emulate_world > 1):
         partition = "single GPU"
     if partition in ("sequences", "kv-range"):
         # one sharded workload as the line's own value
@@ -756,6 +765,9 @@ def main():
                          "split over the ranks).  The default run reports the last two under config.sharded as well.")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-flags", "nccl"], help="kv-range partition: how the states travel")
     ap.add_argument("--no-sharded", action="store_true", help="skip the config.sharded measurements")
+    ap.add_argument("--emulate-world", type=int, default=0, help="with --partition sequences on one GPU: run only the share "
+                    "that rank --emulate-rank of this many ranks would own")
+    ap.add_argument("--emulate-rank", type=int, default=0)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--variant", default="auto", choices=["full", "compact", "auto"], help="CTA shape of the split kernel")
     ap.add_argument("--fuse", action="store_true", help="combine inside the split launch (grid barrier) instead of a separate launch")

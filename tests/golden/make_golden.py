@@ -130,5 +130,7 @@ def main_rope_partial_only(ref_root: str):
 if __name__ == "__main__":
     # `--only-rope-partial` writes that one fixture and leaves the others' bytes alone
     argv = [a for a in sys.argv[1:] if not a.startswith("--")]
-    root = argv[0] if argv else "/root/reference"
+    if not argv:
+        sys.exit("usage: make_golden.py <path of the reference checkout> [--only-rope-partial]")
+    root = argv[0]
     (main_rope_partial_only if "--only-rope-partial" in sys.argv else main)(root)

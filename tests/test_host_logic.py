@@ -215,6 +215,12 @@ def test_fused_rope_launch_list_and_standalone_rotation_launch():
     assert tail[:4] == [0x7300_0000_0000, 0x7300_1000_0000, 0, 128] and tail[4] == mapping()['blk.0.k_proj.output']
     with pytest.raises(CudaSafetyError):
         make_dispatcher(meta128, fuse_append=True, compat=True)
+    # the split kernel copies the new rows 16 bytes at a time: an 8-byte-aligned projection is refused
+    for name in ('blk.0.k_proj.output', 'blk.0.v_proj.output'):
+        skew = dict(mapping())
+        skew[name] += 8
+        with pytest.raises(CudaSafetyError, match="16-byte aligned"):
+            df.build_launches(0, skew, 0x7200_0000_0000)
     with pytest.raises(CudaSafetyError):
         make_dispatcher(dict(meta, rotary_dim=48), fuse_rope=True)
     with pytest.raises(CudaSafetyError):
@@ -408,6 +414,11 @@ def test_slab_allocator_alignment_reuse_and_overlap():
         a.allocate(2 << 20, "huge", MemoryRegion.SCRATCH)
     a.free(z)                  # merges with the 128 B left of y's hole; the merged tail returns to the bump pointer
     assert a.get_stats()["holes"] == 0 and a.current_offset == 384
+    stats = a.get_stats()                                         # the reference's keys (vte/bridge/memory.py:185-193)
+    assert stats["total_bytes"] == 1 << 20 and stats["used_bytes"] == 384 and stats["active_blocks"] == 2
+    assert stats["free_bytes"] == (1 << 20) - 384
+    with pytest.raises(CudaSafetyError):
+        a.initialize()                                            # a second initialize raises, as the reference's does
     big = SlabAllocator(rt, 100 << 20)                            # default 85 % request is capped at 80 %
     assert big.total_size == int((100 << 20) * 0.80)
     a.cleanup()

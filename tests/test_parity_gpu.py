@@ -481,7 +481,7 @@ def test_one_million_context(cuda_runtime, codegen):
 
 @pytest.mark.parametrize("name", ["ragged_d64", "group8_d128", "mha_d128", "outlier_d256"])
 def test_compact_cta_shape_matches(cuda_runtime, codegen, name):
-    """The compact CTA shape (4 consumer warps + 2 loader warps)."""
+    """The compact CTA shape (6 consumer warps + 2 loader warps)."""
     cfg, lens = SMALL_CASES[name]
     q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
     ref = orc.decode_attention(q, k, v, off)
@@ -523,3 +523,48 @@ def test_unsplit_path_stores_the_output_in_one_launch(cuda_runtime, codegen):
         assert ex.dispatcher.max_chunks == 1
     finally:
         ex.cleanup()
+
+
+def test_reference_named_unsplit_kernel(cuda_runtime, codegen):
+    """`flash_attention_kernel` with the reference's 13 arguments and launch geometry
+    (vte/core/kernel_arg_builder.py:57-71; grid (B, Hq, 1), block (head_dim, 1, 1), dynamic
+    shared memory 2 * head_dim * 4): appends this step's K/V rows, attends to every cached
+    position, stores the normalised fp16 output.  Checked against the oracle's append followed
+    by its attention, and the cache rows are read back."""
+    rt = cuda_runtime
+    for name in ("ragged_d64", "group8_d128", "outlier_d256"):
+        cfg, lens = SMALL_CASES[name]
+        q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
+        B, Hq, Hkv, D = cfg.batch, cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+        rng = np.random.default_rng(7)
+        k_new = rng.standard_normal((B, Hkv, D), dtype=np.float32).astype(np.float16)
+        v_new = rng.standard_normal((B, Hkv, D), dtype=np.float32).astype(np.float16)
+        k_ref, v_ref = k.copy(), v.copy()
+        orc.kv_cache_append(k_new, v_new, k_ref, v_ref, off)
+        ref = orc.decode_attention(q, k_ref, v_ref, off)
+        _, fn = codegen.load_kernel_safe(rt, 'flash_attention', rt.get_gpu_architecture(), 'flash_attention_kernel')
+        bufs = []
+
+        def dev(arr):
+            p = rt.safe_malloc(arr.nbytes, "unsplit kernel test output")
+            bufs.append(p)
+            rt.safe_memcpy_host_to_device(p, np.ascontiguousarray(arr), "unsplit kernel test output")
+            return p
+        try:
+            dq, dk, dv, dkc, dvc, doff = dev(q), dev(k_new), dev(v_new), dev(k), dev(v), dev(off)
+            dout = dev(np.zeros((B, Hq, D), np.float16))
+            vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+            args = [vp(dq.value), vp(dk.value), vp(dv.value), vp(dkc.value), vp(dvc.value), vp(dout.value), ci(1), ci(Hq),
+                    ci(Hkv), ci(D), cf(cfg.scale), vp(doff.value), ci(cfg.kv_batch_stride)]
+            rt.launch_kernel(fn, (B, Hq, 1), (D, 1, 1), args, shared_mem=2 * D * 4, expected_args=13)
+            rt.synchronize()
+            out = np.zeros((B, Hq, D), np.float16)
+            rt.safe_memcpy_device_to_host(out, dout, "unsplit kernel test output")
+            assert np.max(np.abs(out.astype(np.float32) - ref)) <= 4e-3, name      # fp16 rounding of outputs up to ~3
+            kc, vc = np.zeros_like(k), np.zeros_like(v)
+            rt.safe_memcpy_device_to_host(kc, dkc, "unsplit kernel test output")
+            rt.safe_memcpy_device_to_host(vc, dvc, "unsplit kernel test output")
+            assert np.array_equal(kc, k_ref) and np.array_equal(vc, v_ref), name
+        finally:
+            for p in bufs:
+                rt.safe_free(p, "unsplit kernel test cleanup")

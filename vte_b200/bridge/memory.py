@@ -51,7 +51,7 @@ class SlabAllocator:
 
     def initialize(self):
         if self._initialized:
-            return
+            raise CudaSafetyError("SlabAllocator is already initialised")     # as vte/bridge/memory.py:55-56
         handle = self._rt.safe_malloc(self.total_size, "VTE_GIANT_SLAB")
         self.slab_base = handle.value if hasattr(handle, "value") else int(handle)
         self._initialized = True
@@ -118,11 +118,15 @@ class SlabAllocator:
         return False
 
     def get_stats(self) -> dict:
+        """The reference's four keys (vte/bridge/memory.py:185-193) plus the number of holes."""
         used = sum(b.aligned_size for b in self.blocks if b.in_use)
-        return {"total": self.total_size, "used": used, "free": self.total_size - used,
-                "blocks": sum(1 for b in self.blocks if b.in_use), "holes": len(self.free_list)}
+        return {"total_bytes": self.total_size, "used_bytes": used, "free_bytes": self.total_size - used,
+                "active_blocks": sum(1 for b in self.blocks if b.in_use), "holes": len(self.free_list)}
 
     def cleanup(self):
+        """Clears the bookkeeping as vte/bridge/memory.py:195-202 does and, unlike it, also hands the
+        slab back: several executors share one runtime in a process here, and the runtime's own
+        cleanup would otherwise be the first to free it."""
         if self._initialized and self.slab_base:
             import ctypes
             self._rt.safe_free(ctypes.c_void_p(self.slab_base), "VTE_GIANT_SLAB")

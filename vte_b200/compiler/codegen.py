@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import hashlib
 import logging
+import os
 import re
 import shutil
 import subprocess
@@ -64,7 +65,14 @@ class CodegenEngine:
 
     @staticmethod
     def _defines(params: dict) -> list[str]:
-        return [f"-D{_sanitize_var(k).upper()}={_sanitize_var(v)}" for k, v in sorted(params.items())]
+        """-D macros from the template parameters, plus (development switch) those named in the
+        environment variable VTEB_KERNEL_DEFINES as `name=value,name=value`; both are sanitised and
+        both enter the cache key."""
+        merged = dict(params)
+        for item in filter(None, os.environ.get("VTEB_KERNEL_DEFINES", "").split(",")):
+            k, _, v = item.partition("=")
+            merged[k.strip()] = int(v) if v.strip().lstrip("-").isdigit() else v.strip()
+        return [f"-D{_sanitize_var(k).upper()}={_sanitize_var(v)}" for k, v in sorted(merged.items())]
 
     def cache_path(self, template_name: str, arch: str, **params) -> Path:
         """cache/<arch>/kernel_<sha256[:16]>.cubin, keyed by every source the

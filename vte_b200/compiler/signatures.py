@@ -8,7 +8,8 @@ kernels list exactly the arguments of
 kv_cache_append.hip.template:13-22,
 flash_attention_split_kv_partial.hip.template:31-45 and
 flash_attention_split_kv_reduce.hip.template:14-22; `rope_kernel` lists those of
-rope.hip.template:17-37 (vte/core/kernel_arg_builder.py:44-56).
+rope.hip.template:17-37 (vte/core/kernel_arg_builder.py:44-56); `flash_attention_kernel` those of
+flash_attention.hip.template:29-43 (vte/core/kernel_arg_builder.py:57-71).
 """
 import ctypes
 
@@ -26,6 +27,7 @@ KERNEL_SIGNATURES = {
     "kv_cache_append_kernel": [P, P, P, P, I, I, P, I],
     "kv_cache_append_rope_kernel": [P, P, P, P, I, I, P, I] + _ROPE_TAIL,
     "rope_kernel": [P, P, P, P, I, I, I, I, P, I, I],
+    "flash_attention_kernel": [P, P, P, P, P, P, I, I, I, I, F, P, I],     # flash_attention.hip.template:29-43
     "flash_attention_split_kv_partial_kernel": _REFERENCE_PARTIAL,
     "flash_attention_split_kv_reduce_kernel": _REDUCE,
     "flash_attention_split_kv_reduce_f32_kernel": _REDUCE,
@@ -57,6 +59,7 @@ KERNEL_SIGNATURES = {
 TEMPLATE_SOURCES = {
     "kv_cache_append": "decode_attention.cu",
     "rope": "decode_attention.cu",
+    "flash_attention": "decode_attention.cu",
     "flash_attention_split_kv_partial": "decode_attention.cu",
     "flash_attention_split_kv_reduce": "decode_attention.cu",
     "decode_attention": "decode_attention.cu",

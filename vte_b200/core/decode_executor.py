@@ -137,6 +137,8 @@ class DecodeAttentionExecutor:
         ctypes.memset(self._stage_out.value, 0, self._out_tail + 256)
         self._graph_exec = None
         self._io_graph_exec = None      # staging copies + the layers' launches + the output copy, as one graph
+        self._stage_event = None        # recorded after a step's staging copies; the next step waits for it
+        self._stage_in_flight = False
         self.kernel_launches_per_step = 0
 
     # ---- data movement helpers ----------------------------------------------------
@@ -244,14 +246,30 @@ class DecodeAttentionExecutor:
         finally:
             self.hip.programmatic_launch = False
 
+    def _wait_for_staging(self):
+        """The pinned staging buffers may be rewritten only after the previous step's asynchronous
+        host-to-device copies have read them (a step enqueued with `read_output=False` returns
+        before they ran)."""
+        if self._stage_in_flight:
+            self.hip.event_synchronize(self._stage_event)
+            self._stage_in_flight = False
+
+    def _mark_staging_copied(self):
+        if self._stage_event is None:
+            self._stage_event = self.hip.event_create()
+        self.hip.event_record(self._stage_event)
+        self._stage_in_flight = True
+
     def _update_staging_buffers(self, kv_offsets: np.ndarray):
         off = np.ascontiguousarray(kv_offsets, dtype=np.int32)
         if off.shape != (self.B,):
             raise CudaSafetyError(f"kv_offsets shape {off.shape} != ({self.B},)")
         if off.min() < 0 or off.max() >= self.S:
             raise CudaSafetyError(f"kv offset outside 0..{self.S - 1}")
+        self._wait_for_staging()
         ctypes.memmove(self._stage_offsets.value, off.ctypes.data, off.nbytes)
         self.hip.memcpy_h2d_async(ctypes.c_void_p(self.offsets.ptr), self._stage_offsets, off.nbytes, "kv_offsets")
+        self._mark_staging_copied()
 
     def launch_step(self):
         """Enqueue one decode step (no host synchronisation)."""
@@ -280,6 +298,7 @@ class DecodeAttentionExecutor:
             qh = np.ascontiguousarray(q_host, dtype=np.float16)
             if qh.nbytes != self.L * self.q_bytes:
                 raise CudaSafetyError("q_host must be [L, B, Hq, D] fp16")
+            self._wait_for_staging()
             ctypes.memmove(self._stage_offsets.value, off.ctypes.data, off.nbytes)
             ctypes.memmove(self._stage_q.value, qh.ctypes.data, qh.nbytes)
             self.hip.graph_launch(self._io_graph_exec)
@@ -294,8 +313,10 @@ class DecodeAttentionExecutor:
                 qh = np.ascontiguousarray(q_host, dtype=np.float16)
                 if qh.nbytes != self.L * self.q_bytes:
                     raise CudaSafetyError("q_host must be [L, B, Hq, D] fp16")
+                # (_update_staging_buffers above already waited for the previous step's copies)
                 ctypes.memmove(self._stage_q.value, qh.ctypes.data, qh.nbytes)
                 self.hip.memcpy_h2d_async(ctypes.c_void_p(self.q_all.ptr), self._stage_q, qh.nbytes, "q staging")
+                self._mark_staging_copied()
             self.launch_step()
             if not read_output:
                 return None
@@ -329,6 +350,10 @@ class DecodeAttentionExecutor:
         return m, l, o
 
     def cleanup(self):
+        if self._stage_event is not None:
+            self.hip.event_destroy(self._stage_event)
+            self._stage_event = None
+            self._stage_in_flight = False
         if self._graph_exec is not None:
             self.hip.graph_exec_destroy(self._graph_exec)
             self._graph_exec = None

@@ -112,9 +112,9 @@ class SplitKVAttentionDispatcher:
         # launch's CTAs to sit beside the split CTA, so the combine starts the moment the split ends
         # and the launch after it is not held back.  Measured on B200, 32k context, one sequence:
         # 10.6 us per layer compact against 12.5 us full; batches of ragged sequences and a
-        # one-million-position sequence run 3 to 18 % slower compact (four warps do not keep up with
-        # a stream that lasts hundreds of microseconds).  "auto" therefore takes compact for one
-        # sequence of up to COMPACT_MAX_CONTEXT positions and full otherwise.
+        # one-million-position sequence run a few percent slower compact (fewer consumer warps do not
+        # keep up with a stream that lasts hundreds of microseconds).  "auto" therefore takes compact
+        # for one sequence of up to COMPACT_MAX_CONTEXT positions and full otherwise.
         if variant not in ("full", "compact", "auto"):
             raise CudaSafetyError(f"variant must be full, compact or auto, not {variant!r}")
         self._plan = None
@@ -382,8 +382,10 @@ class SplitKVAttentionDispatcher:
         if self.fuse_rope or self.fuse_append:
             if not self.fuse_rope:
                 split_tail = [vp(0), vp(0), ci(-1), ci(0)]                 # rotation type -1: none
-            if self.fuse_append and (not k_proj_ptr or not v_proj_ptr or k_proj_ptr % 4 or v_proj_ptr % 4):
-                raise CudaSafetyError("fuse_append: the new K / V rows could not be resolved or are misaligned")
+            # the kernel reads the new rows with 16-byte asynchronous copies (they fill the masked rows of
+            # the sequence's last tile), so they need the same alignment as q and the caches
+            if self.fuse_append and (not k_proj_ptr or not v_proj_ptr or k_proj_ptr % 16 or v_proj_ptr % 16):
+                raise CudaSafetyError("fuse_append: the new K / V rows could not be resolved or are not 16-byte aligned")
             split_tail += [vp(k_proj_ptr if self.fuse_append else 0), vp(v_proj_ptr if self.fuse_append else 0)]
 
         reference_partial_args = [
@@ -402,7 +404,7 @@ class SplitKVAttentionDispatcher:
         items = batch * plan.n_hgroups * C
         n_ctas = max(1, min(items, self.num_sms))
         flags = FLAG_WRITE_EMPTY_O if self.strict_empty_splits else 0
-        flags |= int(os.environ.get('VTEB_EXP_FLAGS', '0'))
+        flags |= FLAG_PREFETCH_Q          # a hint only: Q of a CTA's first item is asked into L2 before the dependency wait
         next_k = next_v = 0
         if self.prefetch_next_layer:
             next_k, next_v = self._resolve_kv_cache_ptrs(layer_idx + 1, {k: v for k, v in tensor_mapping.items()

@@ -36,9 +36,14 @@
 // first wait for their own outstanding copies).
 #pragma once
 
-#ifndef VTEB_PIPELINE_BLOCKS
-#define VTEB_PIPELINE_BLOCKS 1   // 1: two 16-position blocks in flight per consumer warp; 0: one
+#ifndef VTEB_QK_CHAINS
+#define VTEB_QK_CHAINS 2         // independent accumulation chains of the Q K^T product per position half
 #endif
+#ifndef VTEB_PV_LO_ACC
+#define VTEB_PV_LO_ACC 0         // 1: the low parts of P accumulate in registers of their own
+#endif
+constexpr int kQkChains = VTEB_QK_CHAINS;
+constexpr bool kLoAcc = VTEB_PV_LO_ACC != 0;
 
 struct FastArgs {
     const __half* q; const __half* k_cache; const __half* v_cache;
@@ -65,7 +70,7 @@ constexpr int kFlagPrefetchQ = 8;     // ask L2 for the first item's Q rows befo
 
 // ---- optional timeline trace (compiled in with -DVTEB_TRACE=1, used by vte_b200/trace_timeline.py) ----
 // The status word's allocation is then a trace buffer: 64-bit words from byte 256 on,
-// [launch 0..63][traced CTA 0..2][warp 0..9][16 stamps]; per-CTA launch counters sit at byte 64.
+// [launch 0..63][traced CTA 0..2][warp 0..9][32 stamps]; per-CTA launch counters sit at byte 64.
 // Lane 0 of every warp of three CTAs (first, middle, last but two) stamps the SM cycle counter at fixed
 // points, plus %globaltimer at entry and exit so that CTAs and launches can be laid on one axis.
 #ifdef VTEB_TRACE
@@ -313,7 +318,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         __syncthreads();
         if (sel >= 0 && trace_launch < 64)
             tr.base = reinterpret_cast<unsigned long long*>(a.status - 1) + 32 +
-                      (((size_t)trace_launch * 3 + sel) * 10 + (threadIdx.x >> 5)) * 16;
+                      (((size_t)trace_launch * 3 + sel) * 10 + (threadIdx.x >> 5)) * 32;
     }
     VTEB_TR_GT(tr, 0);
     VTEB_TR(tr, 1);
@@ -419,6 +424,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     mbar_arrive(bar);      // no copies belong to this tile
                 }
                 ++filled;
+                if (filled <= 8) VTEB_TR(tr, 11 + filled);
                 if (filled == 1) VTEB_TR(tr, 2);
                 if (filled == nstages) VTEB_TR(tr, 3);
                 if (!stop) VTEB_TR(tr, 4);
@@ -512,6 +518,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         }
         if (!dep_done) grid_dependency_wait();
         asm volatile("cp.async.wait_all;" ::: "memory");
+        VTEB_TR(tr, 8);
+        VTEB_TR_GT(tr, 9);
         return;
     }
 
@@ -556,8 +564,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         __syncwarp();
     };
 
-    float o_acc[NT][2];
-    float m_run = kNeutralM, l_run = 0.f;
+    ConsumerState<NT, kLoAcc> st;
+    st.reset();
     int stage = 0;
     uint32_t full_parity = 0, merge_parity = 0;
     bool merge_pending = false;           // previous item's readers may still use the exchange area
@@ -575,119 +583,6 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                 (hh * (D / 64) + dhalf * (DW / 64)) * blk_bytes + plan.tile * plan.row_bytes;
     const uint32_t v_lane_x = (((lane >> 4) ^ (lane & 7)) << 4);
 
-    // ---- S = Q K^T of one 16-position block: sn[0] positions 0..7, sn[1] positions 8..15 (raw dot
-    // products, unscaled); two accumulation chains each; K fragments are fetched KC k-steps at a time
-    auto qk_block = [&](uint32_t kaddr, float (&sn)[2][2]) {
-        float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, s_alt[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-        constexpr int KC = KS < 8 ? KS : 8;
-#pragma unroll
-        for (int kc = 0; kc < KS; kc += KC) {
-            uint32_t kf[KC][4];
-#pragma unroll
-            for (int i = 0; i < KC; ++i)
-                ldmatrix_x4((kaddr ^ (((kc + i) & 3) << 5)) + ((kc + i) >> 2) * blk_bytes, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
-#pragma unroll
-            for (int i = 0; i < KC; i += 2) {
-                const int ks = kc + i;
-                const uint32_t qa0 = q_frag[(2 * ks) * 32], qa1 = q_frag[(2 * ks + 1) * 32];
-                const uint32_t qb0 = q_frag[(2 * ks + 2) * 32], qb1 = q_frag[(2 * ks + 3) * 32];
-                mma_rows0to7(s[0][0], s[0][1], qa0, qa1, kf[i][0], kf[i][1]);
-                mma_rows0to7(s[1][0], s[1][1], qa0, qa1, kf[i][2], kf[i][3]);
-                mma_rows0to7(s_alt[0][0], s_alt[0][1], qb0, qb1, kf[i + 1][0], kf[i + 1][1]);
-                mma_rows0to7(s_alt[1][0], s_alt[1][1], qb0, qb1, kf[i + 1][2], kf[i + 1][3]);
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < 2; ++n) { sn[n][0] = s[n][0] + s_alt[n][0]; sn[n][1] = s[n][1] + s_alt[n][1]; }
-    };
-
-    // ---- online softmax (log2 domain) of a block's raw scores and O += P V; `left` = positions of
-    // the block that belong to the item (may exceed 16), the rest are masked
-    auto softmax_pv = [&](const float (&sraw)[2][2], uint32_t vaddr, int left) {
-        // V fragments do not depend on the softmax: fetch the first 64 columns now
-        constexpr int VC = 4;                 // ldmatrix.x4.trans per chunk = 64 output columns
-        constexpr int NVC = NT / (2 * VC);    // chunks
-        uint32_t vf[2][VC][4];
-#pragma unroll
-        for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr ^ (i << 5), vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
-        float s[2][2];
-        float mx = kNeutralM;
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const bool valid = (n * 8 + 2 * t + j) < left;
-                s[n][j] = valid ? sraw[n][j] * scale2 : kNeutralM;
-                mx = fmaxf(mx, s[n][j]);
-            }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float corr = fast_exp2(m_run - m_new);
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
-            l_run *= corr;
-#pragma unroll
-            for (int n = 0; n < NT; ++n) { o_acc[n][0] *= corr; o_acc[n][1] *= corr; }
-        }
-        m_run = m_new;
-        float p[2][2];
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const bool valid = (n * 8 + 2 * t + j) < left;
-                p[n][j] = valid ? fast_exp2(s[n][j] - m_new) : 0.f;
-            }
-        l_run += (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
-        // P = P_hi + P_lo, both fp16: keeps ~22 bits of each probability.
-        uint32_t ph[2], pl[2];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const __half2 hi = __floats2half2_rn(p[n][0], p[n][1]);
-            const float2 hif = __half22float2(hi);
-            ph[n] = *reinterpret_cast<const uint32_t*>(&hi);
-            pl[n] = pack_half2(p[n][0] - hif.x, p[n][1] - hif.y);
-        }
-        // O += P V, 64 columns per chunk; the next chunk's fragments load meanwhile
-#pragma unroll
-        for (int ch = 0; ch < NVC; ++ch) {
-            if (ch + 1 < NVC) {
-#pragma unroll
-                for (int i = 0; i < VC; ++i)
-                    ldmatrix_x4_trans((vaddr ^ (i << 5)) + (ch + 1) * blk_bytes, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
-                                      vf[(ch + 1) & 1][i][2], vf[(ch + 1) & 1][i][3]);
-            }
-#pragma unroll
-            for (int i = 0; i < VC; ++i) {
-                const int n = 2 * (ch * VC + i);
-                float e0, e1, f0, f1;
-                mma_hi_lo(o_acc[n][0], o_acc[n][1], e0, e1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][0], vf[ch & 1][i][1]);
-                mma_hi_lo(o_acc[n + 1][0], o_acc[n + 1][1], f0, f1, ph[0], pl[0], ph[1], pl[1], vf[ch & 1][i][2], vf[ch & 1][i][3]);
-                // rows 8..15 of A carried P_lo; their product belongs to this thread's row too
-                o_acc[n][0] += e0; o_acc[n][1] += e1; o_acc[n + 1][0] += f0; o_acc[n + 1][1] += f1;
-            }
-        }
-    };
-
-    // Two blocks are in flight per warp: the scores of block i+1 are issued before the softmax and
-    // the P V product of block i, so the tensor pipe works on one block while the other goes through
-    // the shuffle / exp chain.  `pend_*` describe the block whose scores are known and whose softmax
-    // and P V are still to come; the stage that holds it is handed back only after its V rows were read.
-    float pend_s[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    uint32_t pend_vaddr = 0;
-    int pend_left = 0;
-    bool pending = false;
-    int held_stage = -1;                  // stage whose release waits for the pending block (-1: none)
-    auto finish_pending = [&]() {
-        softmax_pv(pend_s, pend_vaddr, pend_left);
-        pending = false;
-        if (held_stage >= 0) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * held_stage);
-            held_stage = -1;
-        }
-    };
-
     // The first item is known without the loader: fetch its Q while the first tile is in flight.
     grid_dependency_wait();
     VTEB_TR(tr, 2);
@@ -695,6 +590,8 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     VTEB_TR(tr, 3);
 #ifdef VTEB_TRACE
     bool trace_first_full = true;
+    int trace_tile = 0;
+    long long trace_wait = 0;
 #endif
 
     for (;;) {
@@ -706,8 +603,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             return;
         }
 #ifdef VTEB_TRACE
-        VTEB_TR_ADD(tr, 11, clock64() - trace_w0);
+        trace_wait += clock64() - trace_w0;
         if (trace_first_full) { VTEB_TR(tr, 4); trace_first_full = false; }
+        if (trace_tile < 8) VTEB_TR(tr, 12 + trace_tile);
 #endif
         full_parity ^= (1u << stage);
         const TileHeader* hd = headers + stage;
@@ -719,47 +617,32 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         const int nvalid = hd->nvalid, blk0 = hd->blk0;
 
         if (flags & kTileFirst) {
-            // (no block is pending here: an item's last tile finishes it)
-            m_run = kNeutralM; l_run = 0.f;
-#pragma unroll
-            for (int n = 0; n < NT; ++n) { o_acc[n][0] = 0.f; o_acc[n][1] = 0.f; }
+            st.reset();
             if (!first_item) load_q(item_b, item_hgroup);
             first_item = false;
         }
 
         const uint32_t tile_base = smem_u32(stages + (size_t)stage * plan.stage_bytes);
         if (flags & kTileFirst) next_blk = sub;
-        bool pend_here = false;               // the pending block lies in this tile
         for (; next_blk < blk0 + blocks_per_tile; next_blk += plan.wph) {
             const int r0 = (next_blk - blk0) * kBlockPos;
             if (r0 >= nvalid) break;
             float sn[2][2];
-            qk_block((tile_base + r0 * 128 + k_lane_off) | k_lane_x, sn);
-#if !VTEB_PIPELINE_BLOCKS
-            softmax_pv(sn, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, nvalid - r0);
-            continue;
-#endif
-            if (pending) finish_pending();
-#pragma unroll
-            for (int n = 0; n < 2; ++n) { pend_s[n][0] = sn[n][0]; pend_s[n][1] = sn[n][1]; }
-            pend_vaddr = (tile_base + r0 * 128 + v_lane_off) | v_lane_x;
-            pend_left = nvalid - r0;
-            pending = true;
-            pend_here = true;
+            qk_block<D, kQkChains>(q_frag, (tile_base + r0 * 128 + k_lane_off) | k_lane_x, blk_bytes, sn);
+            softmax_pv<NT, kLoAcc>(st, sn, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, blk_bytes, nvalid - r0, scale2, t);
         }
         if (flags & kTileLast) {
-            if (pending) finish_pending();
-            pend_here = false;
+            st.fold_lo();
             VTEB_TR(tr, 5);
         }
 
-        // Hand the stage back to the loader, unless the pending block still needs its V rows.
-        if (pend_here) {
-            held_stage = stage;
-        } else {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
-        }
+#ifdef VTEB_TRACE
+        if (trace_tile < 8) VTEB_TR(tr, 20 + trace_tile);
+        ++trace_tile;
+#endif
+        // Hand the stage back to the loader.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * stage);
 
         if (flags & kTileLast) {
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
@@ -767,7 +650,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, 2 unused
             if (plan.wph == 1) {
                 // One warp per KV head: nothing to merge, the warp stores its own state.
-                float l_own = l_run;
+                float l_own = st.l;
                 l_own += __shfl_xor_sync(0xffffffffu, l_own, 1);
                 l_own += __shfl_xor_sync(0xffffffffu, l_own, 2);
                 const bool empty1 = (flags & kTileEmpty) != 0;
@@ -779,7 +662,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 #pragma unroll
                     for (int n = 0; n < NT; ++n)
                         store_out2(a.output, a.out_kind, row * D + dhalf * DW + n * 8 + 2 * t,
-                                   make_float2(o_acc[n][0] * inv, o_acc[n][1] * inv));
+                                   make_float2(st.o[n][0] * inv, st.o[n][1] * inv));
                 } else if (g < group) {
                     const long long stat = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
                                             (long long)hh * group + g) * a.max_chunks + item_c;
@@ -787,10 +670,10 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         float* out = a.partial_o + stat * D + dhalf * DW + 2 * t;
 #pragma unroll
                         for (int n = 0; n < NT; ++n)
-                            *reinterpret_cast<float2*>(out + n * 8) = make_float2(o_acc[n][0], o_acc[n][1]);
+                            *reinterpret_cast<float2*>(out + n * 8) = make_float2(st.o[n][0], st.o[n][1]);
                     }
                     if (t == 0 && dhalf == 0) {
-                        a.partial_m[stat] = empty1 ? kNeutralM : m_run * kLn2;
+                        a.partial_m[stat] = empty1 ? kNeutralM : st.m * kLn2;
                         a.partial_l[stat] = empty1 ? 0.f : l_own;
                     }
                 }
@@ -804,15 +687,15 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 }
                 merge_parity ^= 2u;
             }
-            float l_quad = l_run;
+            float l_quad = st.l;
             l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 1);
             l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 2);
             if (g < group) {
                 float* dst = merge + ((size_t)warp * group + g) * pitch;
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
-                    *reinterpret_cast<float2*>(dst + dhalf * DW + n * 8 + 2 * t) = make_float2(o_acc[n][0], o_acc[n][1]);
-                if (t == 0) { dst[D + 4] = m_run; dst[D + 5] = l_quad; }
+                    *reinterpret_cast<float2*>(dst + dhalf * DW + n * 8 + 2 * t) = make_float2(st.o[n][0], st.o[n][1]);
+                if (t == 0) { dst[D + 4] = st.m; dst[D + 5] = l_quad; }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(merge_bar0);
@@ -899,6 +782,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     VTEB_TR(tr, 8);
     VTEB_TR_GT(tr, 9);
+#ifdef VTEB_TRACE
+    if (tr.base != nullptr && lane == 0) tr.base[11] = (unsigned long long)trace_wait;
+#endif
     if (kCompact || a.out_kind == 0 || (a.flags & kFlagDirectOutput)) return;
     // ===================================================================== in-launch combine
     // (needs all eight consumer warps; the host only asks for it then)

@@ -21,7 +21,7 @@ from .compiler import CodegenEngine
 from .core.decode_executor import DecodeAttentionExecutor
 from .workloads import CONFIGS, draw_context_lengths
 
-TRACE_BYTES = 512 << 10
+TRACE_BYTES = 1 << 20
 CONSUMER = ["gt_entry", "entry", "dep_wait", "q_loaded", "first_tile", "blocks_done", "merge_bar", "stored", "exit", "gt_exit"]
 LOADER = ["gt_entry", "entry", "tile1_issued", "stages_full", "last_issue", "dep_wait", "-", "-", "exit", "gt_exit"]
 
@@ -81,8 +81,15 @@ def main(argv=None) -> int:
     rt.synchronize()
     buf = np.zeros(TRACE_BYTES // 8, dtype=np.uint64)
     rt.safe_memcpy_device_to_host(buf, trace, "trace output")
-    split = buf[32:32 + 64 * 3 * 10 * 16].reshape(64, 3, 10, 16).astype(np.int64)
-    comb = buf[32 + 64 * 3 * 10 * 16:32 + 64 * 3 * 10 * 16 + 64 * 2 * 4].reshape(64, 2, 4).astype(np.int64)
+    n_split = 64 * 3 * 10 * 32
+    split = buf[32:32 + n_split].reshape(64, 3, 10, 32).astype(np.int64)
+    comb = buf[32 + n_split:32 + n_split + 64 * 2 * 4].reshape(64, 2, 4).astype(np.int64)
+    # %globaltimer values are ~2^61 ns: subtract the origin while they are still integers
+    origin = int(split[a.first, 0, 0, 0])
+    for arr, slots in ((split, (0, 9)), (comb, (0, 1, 2))):
+        for k in slots:
+            nz = arr[..., k] != 0
+            arr[..., k][nz] -= origin
     plan = ex.dispatcher._plan
     n_warps = plan.threads // 32
     cw = n_warps - 2
@@ -90,17 +97,22 @@ def main(argv=None) -> int:
     def to_us(w):
         """Stamps of one warp on the global time axis (ns -> us), cycle stamps converted with the
         warp's own entry/exit pair of both clocks."""
-        gt0, c0, c1, gt1 = w[0], w[1], w[8], w[9]
+        gt0, c0, c1, gt1 = int(w[0]), int(w[1]), int(w[8]), int(w[9])
         f = (gt1 - gt0) / max(1, c1 - c0)
         out = [gt0 / 1e3]
         for k in range(1, 9):
-            out.append((gt0 + (w[k] - c0) * f) / 1e3 if w[k] else float("nan"))
+            out.append((gt0 + (int(w[k]) - c0) * f) / 1e3 if w[k] else float("nan"))
         out.append(gt1 / 1e3)
-        return out, f
+        tiles = []
+        for i in range(8):
+            if w[12 + i]:
+                tiles.append(((gt0 + (int(w[12 + i]) - c0) * f) / 1e3,
+                              (gt0 + (int(w[20 + i]) - c0) * f) / 1e3 if w[20 + i] else float("nan")))
+        return out, f, tiles
 
     print(f"{a.workload} variant={a.variant} defines={defines} compact={ex.dispatcher.compact} "
           f"splits={ex.dispatcher.max_chunks} warps={n_warps} stages={plan.nstages} tile={plan.tile}")
-    base = split[a.first, 0, 0, 0] / 1e3
+    base = 0.0
     for l in range(a.first, min(L, a.first + a.count)):
         print(f"--- launch {l} (times in us since CTA 0 entered launch {a.first})")
         for sel, name in enumerate(("first CTA", "middle CTA", "last-but-two CTA")):
@@ -108,10 +120,14 @@ def main(argv=None) -> int:
                 st = split[l, sel, w]
                 if st[0] == 0:
                     continue
-                us, f = to_us(st)
+                us, f, tiles = to_us(st)
                 names = CONSUMER if w < cw else LOADER
                 cells = " ".join(f"{n}={u - base:7.2f}" for n, u in zip(names[1:], us[1:]) if n != "-" and u == u)
                 extra = f" wait_cycles={st[11]}" if w < cw else ""
+                if w < cw:
+                    extra += " tiles(ready>done): " + " ".join(f"{x - base:.2f}>{y - base:.2f}" for x, y in tiles)
+                elif w == cw:
+                    extra += " tile issues: " + " ".join(f"{x - base:.2f}" for x, _ in tiles)
                 print(f"  {name:17s} warp {w} ({'consumer' if w < cw else 'K loader' if w == cw else 'V loader'}) "
                       f"{cells}{extra} [{1e3 / f if f else 0:.0f} MHz]")
         for sel, name in enumerate(("first", "last")):
