@@ -367,6 +367,29 @@ def measure_kv_range(args, rt, rdzv, rank, world, exchange, n_layers, steps, wor
     lengths = np.array([total], dtype=np.int32)
     bytes_all = algorithmic_bytes(cfg, lengths) * n_layers
     name = f"{workload}: 1 x {cfg.num_q_heads} query / {cfg.num_kv_heads} KV heads of {cfg.head_dim}, context {total}, {n_layers} layer(s) per step"
+    if world == 1 and getattr(args, "emulate_world", 0) > 1:
+        # one rank's share of an N-rank run without its peers: split + state combine + merge of the one
+        # local state; what is left of the N-rank time is the exchange
+        shard = total // args.emulate_world
+        sh = KVRangeShardedDecode(rt, CodegenEngine(), metadata(cfg), shard, n_layers, None, exchange="nccl", rendezvous=rdzv)
+        try:
+            for l in range(n_layers):
+                sh.ex.fill_cache_on_device(l, cfg.base_seed * 1000 + l, cfg.sigma_kv)
+                rng = np.random.default_rng([cfg.base_seed, l, 99])
+                sh.ex.upload_layer(l, rng.standard_normal((1, cfg.num_q_heads, cfg.head_dim), dtype=np.float32).astype(np.float16))
+            sh.execute_decode(shard - 1)
+            for _ in range(3):
+                sh.launch_step()
+            t = timed_trials(rt, rdzv, sh.launch_step, steps)
+            step_s = t["median_ms"] / 1e3
+            share = algorithmic_bytes(cfg, np.array([shard], dtype=np.int32)) * n_layers
+            return {"workload": name, "partition": f"one rank's share of {args.emulate_world} ({shard} positions) alone on one GPU: "
+                                                   "split + state combine + merge of the local state, no exchange",
+                    "n_gpus": 1, "value": share / step_s / 1e12, "unit": UNIT, "us_per_layer_step": step_s * 1e6 / n_layers,
+                    "ms_per_step": t["median_ms"], "splits": sh.ex.dispatcher.max_chunks,
+                    "kernels": "fast, compact CTAs" if sh.ex.dispatcher.compact else "fast, full CTAs"}
+        finally:
+            sh.cleanup()
     if world == 1:
         ex = DecodeAttentionExecutor(rt, CodegenEngine(), metadata(cfg), 1, total, n_layers, output_f32=True, variant=args.variant)
         try:
@@ -485,7 +508,7 @@ def run_ours(args, rank, world, local_rank):
     rt = CudaRuntime(device_index=local_rank)
     rt.initialize()
     partition = args.partition or "replicas"
-    if world == 1 and not (partition == "sequences" and args.emulate_world > 1):
+    if world == 1 and not (partition in ("sequences", "kv-range") and args.emulate_world > 1):
         partition = "single GPU"
     if partition in ("sequences", "kv-range"):
         # one sharded workload as the line's own value

@@ -386,7 +386,7 @@ def test_split_count_policy():
     assert choose_split_count(148, 1, 2, 32768) == 74
     assert choose_split_count(148, 64, 1, 16384) == 16            # ragged batch: ~4 items per SM -> 1024-position chunks
     assert choose_split_count(148, 16, 1, 65536) == 64
-    assert choose_split_count(148, 4, 1, 4096) == 16              # small batch: 256-position chunks
+    assert choose_split_count(148, 4, 1, 4096) == 8               # small batch: 512-position chunks, the smallest aimed at
     assert choose_split_count(148, 2, 1, 100) == 1
 
 

@@ -29,7 +29,7 @@ from ..config import ENV_COMPAT_KERNELS, ENV_DISABLE_SPLITKV
 
 SPLIT_KV_CHUNK_SIZE = 32          # the reference's historical chunk (RX 7600, 32 CUs)
 MAX_SPLITS = 256
-TARGET_CHUNK_POSITIONS = 256      # smallest chunk length aimed at when many sequences share the GPU
+TARGET_CHUNK_POSITIONS = 512      # smallest chunk length aimed at when many sequences share the GPU
 FLAG_WRITE_EMPTY_O = 1
 FLAG_DIRECT_OUTPUT = 2
 FLAG_TENSOR_MAPS = 4
@@ -47,11 +47,14 @@ def _chunk_size_for_cus(num_cus: int) -> int:
 
 
 def choose_chunk_positions(num_sms: int, batch: int, n_hgroups: int, context_length: int) -> int:
-    """Positions per split aimed at when several sequences share the GPU: about four
-    work items per SM if every sequence were half the configured context, as a power of
-    two within [256, 2048].  Measured on B200: a work item costs a few microseconds of
-    fixed time (cross-warp merge, next item's Q fetch), so 256-position items reach
-    2.9 TB/s on the 16 x (2 KV heads of 256) workload where 2048-position items reach 4.1."""
+    """Positions per split aimed at when several sequences share the GPU: about four work items per
+    SM if every sequence were half the configured context, as a power of two within [512, 2048].
+    Measured on B200: a work item costs a few microseconds of fixed time (its Q rows, the cross-warp
+    merge, the ragged last tile), which outweighs the better balance of small items.  Per layer, with
+    256 / 512 / 1024 / 2048-position items: the 64-sequence ragged batch of 8 x 64-wide heads
+    - / - / 191 / 203 us, its 16-sequence share 61.4 / 60.4 / 62.2 / 71.2 us, its 8-sequence share
+    37.7 / 34.8 / 39.2 / - us; two sequences of 2 x 256-wide heads 36.9 / 32.0 / 35.7 / - us, sixteen
+    - / - / 208 / 201 us."""
     est_positions = batch * n_hgroups * max(1, context_length // 2)
     target = est_positions / max(1, num_sms * 4)
     chunk = TARGET_CHUNK_POSITIONS
