@@ -166,7 +166,7 @@ def test_ragged_batch_matches_oracle(cuda_runtime, codegen):
     q, k, v, off = make_layer_inputs(cfg, 0)
     ref = orc.decode_attention(q, k, v, off)
     out, _, C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off)
-    assert C == 16
+    assert C == 8                  # 512-position work items, the smallest the dispatcher aims at
     assert_parity(out, ref, tight=5e-5)
     out2, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=64, min_chunk=64)
     assert_parity(out2, ref, tight=5e-5)

@@ -409,15 +409,14 @@ __device__ __forceinline__ void combine_sync() {
     else __syncthreads();
 }
 
-// Partials are always read with L2-only loads: the combine's CTAs are resident while the split launch
-// is still writing them (programmatic dependent launch, and the warm-up pass below touches them before
-// the dependency wait), so nothing of them may be served from this SM's L1.
 template <bool kFused>
-__device__ __forceinline__ float combine_ld(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float combine_ld(const float* p) { return kFused ? __ldcg(p) : *p; }
 template <bool kFused>
-__device__ __forceinline__ float4 combine_ld4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 combine_ld4(const float* p) {
+    return kFused ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p);
+}
 
-// out_kind: 1 = fp16 output, 2 = fp32 output, 3 = unnormalised shard state [D + 2] per row, 0 = store nothing
+// out_kind: 1 = fp16 output, 2 = fp32 output, 3 = unnormalised shard state [D + 2] per row
 template <bool kFused>
 __device__ __forceinline__ void combine_slice(
     const float* __restrict__ partial_m, const float* __restrict__ partial_l,
@@ -497,9 +496,7 @@ __device__ __forceinline__ void combine_slice(
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) s += flat[w * 32 + tid];
-        if (out_kind == 0) {
-            // warm-up pass: nothing is stored
-        } else if (out_kind == 3) {
+        if (out_kind == 3) {
             // unnormalised state of this shard: o[D], then m (natural-log units), then l
             float* st = reinterpret_cast<float*>(output) + (long long)bh * (head_dim + 2);
             st[dpart * 32 + tid] = s;
@@ -512,13 +509,6 @@ __device__ __forceinline__ void combine_slice(
         }
     }
 }
-
-// 1: the combine's CTAs, which sit on their SMs waiting for the split launch anyway, first walk once
-// through the merge arithmetic on one row (result discarded), so that the real pass finds its
-// instructions cached.  Measured at 32k context, one sequence: 0.19 us per layer.
-#ifndef VTEB_COMBINE_WARM
-#define VTEB_COMBINE_WARM 1
-#endif
 
 __device__ __forceinline__ void fast_combine_kernel_body(
     const float* __restrict__ partial_m, const float* __restrict__ partial_l,
@@ -538,13 +528,6 @@ __device__ __forceinline__ void fast_combine_kernel_body(
     }
 #endif
     grid_launch_dependents();
-#if VTEB_COMBINE_WARM
-    // Parked before the dependency anyway: walk once through the merge on one split of this slice (the
-    // values may still be changing and the result goes nowhere), so that the instructions are in the SM's
-    // caches when the real pass starts.
-    combine_slice<false>(partial_m, partial_l, partial_o, nullptr, 0, head_dim, 1, dsplit, blockIdx.x, combine_weight_sh);
-    __syncthreads();
-#endif
     grid_dependency_wait();
 #ifdef VTEB_TRACE
     if (ctr) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ctr[1]));
