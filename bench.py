@@ -60,6 +60,7 @@ MIN_TRIAL_MS = 50.0
 # (workload, compact CTA shape).  A rebuilt kernel has another hash and reports traffic null until it
 # is captured again.
 NCU_TRAFFIC_BYTES: dict[str, dict[tuple[str, bool], int]] = {
+    "7d9d3e29a69b367e": {("c2", True): 33622528},      # 33.62 MB read + <= 256 B written, three launches of the 8-layer case
 }
 
 
@@ -587,15 +588,15 @@ def run_ours(args, rank, world, local_rank):
     rt.synchronize()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    t = timed_trials(rt, rdzv, ex.launch_step, args.steps)
+    t = timed_trials(rt, rdzv, ex.launch_step, args.steps, trials=args.trials, min_trial_ms=args.min_trial_ms)
     ex.dispatcher_check()
 
     # ---- end to end through the public call: host Q + offsets in, outputs back, every step
     for _ in range(3):
         ex.execute_decode_batch(offsets, q_host=q_all)
     e2e_trials = []
-    e2e_steps = max(args.steps, int(math.ceil(MIN_TRIAL_MS / max(t["median_ms"], 1e-3))))
-    for _ in range(TRIALS):
+    e2e_steps = max(args.steps, int(math.ceil(args.min_trial_ms / max(t["median_ms"], 1e-3))))
+    for _ in range(args.trials):
         rdzv.barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
@@ -604,8 +605,9 @@ def run_ours(args, rank, world, local_rank):
     e2e_s = statistics.median(e2e_trials)
 
     # ---- per-kernel durations: the same launches with an event before and after each kind of kernel
-    kern = kernel_durations(rt, ex, n_layers, reps=20)
-    probe_us = read_probe_us(rt, ex, n_layers, reps=20) if cfg.batch == 1 else None
+    reps = 20 if args.min_trial_ms > 0 else 2
+    kern = kernel_durations(rt, ex, n_layers, reps=reps)
+    probe_us = read_probe_us(rt, ex, n_layers, reps=reps) if cfg.batch == 1 else None
     clocks = sampler.stop()
 
     result = None
@@ -644,7 +646,7 @@ def run_ours(args, rank, world, local_rank):
                     "h2d_bytes_per_step": int(q_all.nbytes + offsets.nbytes),
                     "d2h_bytes_per_step": int(n_layers * ex.out_bytes),
                     "ms_per_step": e2e_s * 1e3, "ms_per_step_min_max": [min(e2e_trials) * 1e3, max(e2e_trials) * 1e3],
-                    "steps_per_trial": e2e_steps, "trials": TRIALS,
+                    "steps_per_trial": e2e_steps, "trials": args.trials,
                     "note": "KV cache is persistent device state, as in the reference's executors; per step the host "
                             "sends every layer's Q and the kv offsets and reads every layer's output"},
             "gpu_launches": ex.kernel_launches_per_step * args.steps,
@@ -788,6 +790,9 @@ def main():
                          "split over the ranks).  The default run reports the last two under config.sharded as well.")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-flags", "nccl"], help="kv-range partition: how the states travel")
     ap.add_argument("--no-sharded", action="store_true", help="skip the config.sharded measurements")
+    ap.add_argument("--trials", type=int, default=TRIALS, help="timed trials (median reported)")
+    ap.add_argument("--min-trial-ms", type=float, default=MIN_TRIAL_MS,
+                    help="a trial replays a multiple of --steps until it lasts this long (0: exactly --steps; for profiler runs)")
     ap.add_argument("--emulate-world", type=int, default=0, help="with --partition sequences on one GPU: run only the share "
                     "that rank --emulate-rank of this many ranks would own")
     ap.add_argument("--emulate-rank", type=int, default=0)
