@@ -460,23 +460,23 @@ def measure_kv_range(args, rt, rdzv, rank, world, exchange, n_layers, steps, wor
 
 
 def guarded(rdzv, fn, *a, **k):
-    """Runs one sharded measurement; a failure becomes an `error` record on every rank instead of
-    ending the run (the ranks agree on the outcome through the rendezvous)."""
-    err = ""
-    rec = None
+    """Runs one sharded measurement; a failure becomes an `error` record instead of ending the run.
+    A rank that fails closes its rendezvous sockets, so the ranks blocked in a collective with it fail
+    at once (instead of waiting for a timeout) and the remaining sharded measurements are skipped."""
+    if getattr(rdzv, "broken", False):
+        return {"skipped": "an earlier sharded measurement failed on some rank"}
     try:
         rec = fn(*a, **k)
+        errs = [x.decode() for x in rdzv.allgather(b"")]
+        if not any(errs):
+            return rec
+        err = "; ".join(f"rank {r}: {x}" for r, x in enumerate(errs) if x)
     except Exception as e:                                   # noqa: BLE001
         err = f"{type(e).__name__}: {e}"
         traceback.print_exc(file=sys.stderr)
-    try:
-        errs = [x.decode() for x in rdzv.allgather(err.encode())]
-    except Exception as e:                                   # noqa: BLE001
-        return {"error": f"rendezvous lost after: {err or e}"}
-    bad = [f"rank {r}: {x}" for r, x in enumerate(errs) if x]
-    if bad:
-        return {"error": "; ".join(bad)[:600]}
-    return rec
+    rdzv.broken = True
+    rdzv.close()
+    return {"error": err[:600]}
 
 
 def sharded_block(args, rt, rdzv, rank, world):
@@ -503,7 +503,7 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         vbuild.build_library()
         vbuild.build_cubins()
-    rdzv = Rendezvous.from_env(timeout_s=300.0) if world > 1 else Rendezvous(0, 1)
+    rdzv = Rendezvous.from_env(timeout_s=120.0) if world > 1 else Rendezvous(0, 1)
     rdzv.barrier()
 
     rt = CudaRuntime(device_index=local_rank)
@@ -525,8 +525,9 @@ def run_ours(args, rank, world, local_rank):
                     "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": rec}
             print(json.dumps(line), flush=True)
         rt.cleanup()
-        rdzv.barrier()
-        rdzv.close()
+        if not getattr(rdzv, "broken", False):
+            rdzv.barrier()
+            rdzv.close()
         return 0
 
     cfg = CONFIGS[args.workload]
@@ -686,8 +687,9 @@ def run_ours(args, rank, world, local_rank):
                       f"tools/validate_attention.py::ref_gqa_attention, host has {os.cpu_count()} cores",
             "ms_per_layer": best * 1e3 / sample_layers}
     rt.cleanup()
-    rdzv.barrier()
-    rdzv.close()
+    if not getattr(rdzv, "broken", False):
+        rdzv.barrier()
+        rdzv.close()
     if rank == 0:
         print(json.dumps(result), flush=True)
     return 0

@@ -55,3 +55,31 @@ def test_shard_ranges_partition_exactly():
     assert sequences_of_rank(64, 3, 8) == (24, 32)
     with pytest.raises(ValueError):
         kv_range_of_rank(10, 2, 2)
+
+
+def test_bench_sharding_helpers():
+    """Pieces of bench.py's sharded block that need no GPU: the longest-first deal of sequences to
+    ranks, and the guard that turns one rank's failure into the same error record on every rank."""
+    import importlib.util
+    import numpy as np
+    from pathlib import Path
+    spec = importlib.util.spec_from_file_location("bench_module", Path(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    from vte_b200.bridge.rendezvous import Rendezvous
+    from vte_b200.workloads import CONFIGS, draw_context_lengths
+
+    lengths = draw_context_lengths(CONFIGS["c3"])
+    for world in (2, 4, 8):
+        parts = bench.balanced_assignment(lengths, world)
+        assert sorted(int(b) for p in parts for b in p) == list(range(64))          # every sequence exactly once
+        assert all(len(p) == 64 // world for p in parts)
+        loads = [int(lengths[p].astype(np.int64).sum()) for p in parts]
+        assert max(loads) / (sum(loads) / world) < 1.03                              # contiguous blocks: up to 1.27
+    rdzv = Rendezvous(0, 1)
+    assert bench.guarded(rdzv, lambda: {"value": 1.0}) == {"value": 1.0}
+
+    def boom():
+        raise RuntimeError("no device")
+    rec = bench.guarded(rdzv, boom)
+    assert "error" in rec and "no device" in rec["error"]
