@@ -333,10 +333,11 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // ===================================================================== K loader
     if (warp == kLoaderWarpK) {
-        if ((a.flags & kFlagPrefetchQ) && lane == 0 && (int)blockIdx.x < total_items) {
+        if ((a.flags & kFlagPrefetchQ) && lane == 0 && (int)blockIdx.x < total_items && first_geom.c == 0) {
             // Q of the first item is read right after the dependency wait; when it is not in L2 by then
             // (nothing produced it recently) the consumers start a DRAM latency late.  A prefetch moves no
             // data into the SM, so it may run ahead of the kernel that writes Q: L2 is where that write lands.
+            // Only the CTA that owns split 0 of a (sequence, head group) asks: the others share its rows.
             const __half* q0 = a.q + ((long long)first_geom.b * a.num_q_heads + (long long)first_geom.hgroup * plan.hg * group) * D;
             const unsigned qbytes = (unsigned)(plan.hg * group * D * 2);
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(q0), "r"(qbytes) : "memory");
@@ -351,7 +352,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             ItemGeometry g = first_geom;
             if (!stop && item != (int)blockIdx.x) g = decode_item(a, plan, item);
             const int ntiles = stop ? 1 : max(1, (g.end - g.start + plan.tile - 1) / plan.tile);
-            if ((a.flags & kFlagPrefetchQ) && !stop && item != (int)blockIdx.x && g.end > g.start && lane == 0) {
+            if ((a.flags & kFlagPrefetchQ) && !stop && item != (int)blockIdx.x && g.c == 0 && g.end > g.start && lane == 0) {
                 // a later item: the loader runs several tiles ahead of the consumers, so asking L2 for the
                 // item's Q rows now means their loads at the item's first tile do not go to DRAM
                 const __half* qn = a.q + ((long long)g.b * a.num_q_heads + (long long)g.hgroup * plan.hg * group) * D;
