@@ -19,13 +19,17 @@
 // numbers.
 //
 // Consumer warp w: KV head (w % hg) of the group, every wph-th 16-position
-// block.  Per block: S = Q K^T with mma.sync m16n8k16 (Q rows are the query
+// block.  Per block (consumer_block.cuh): S = Q K^T with mma.sync m16n8k16 (Q rows are the query
 // heads of the KV head, K fragments via ldmatrix), online softmax in the log2
 // domain on the accumulator fragment, P split into an fp16 high and low part
 // (high part in rows 0..7 of the A operand, low part in rows 8..15, so one mma
 // multiplies both), O += P V with V fragments via ldmatrix.trans.  At the end of an item the
 // warps of a KV head exchange (m, l, o) through shared memory and the merged
 // state is stored to partial_m / partial_l / partial_o.
+//
+// Under programmatic dependent launch everything that does not depend on the previous launch runs
+// before griddepcontrol.wait: barrier set-up, the first item's geometry (kv offsets, sequence order),
+// the K/V tiles of positions older than the newest one, and an L2 prefetch of the first item's Q rows.
 //
 // The rotating variants (`..._rope_...`) rotate Q while loading it and, when handed this step's K
 // and V projections, also do the cache append: the loader warps of the CTA whose tile ends with a
@@ -41,6 +45,13 @@
 #endif
 #ifndef VTEB_PV_LO_ACC
 #define VTEB_PV_LO_ACC 0         // 1: the low parts of P accumulate in registers of their own
+#endif
+// (KV head, query row) pairs a warp merges per pass at the end of an item, for heads up to 128 wide
+// (256-wide heads always take one): 2 = one pair per half-warp.  Measured with 12 query heads on six
+// warps (one pass instead of two): the 32k-context layer 10.13 against 10.40 us, its split kernel alone
+// 9.34 against 9.80 us per launch.
+#ifndef VTEB_MERGE_PAIRS
+#define VTEB_MERGE_PAIRS 2
 #endif
 constexpr int kQkChains = VTEB_QK_CHAINS;
 constexpr bool kLoAcc = VTEB_PV_LO_ACC != 0;
@@ -58,8 +69,9 @@ struct FastArgs {
     // tensor maps over the K and V caches (rows = positions of all sequences, 64-half boxes of
     // `tile` rows, 128-byte swizzle); used for whole tiles when kFlagTensorMaps is set
     const KvTensorMap* tmap_k; const KvTensorMap* tmap_v;
-    // fused append (rotating kernels only): this step's K and V projections [B, Hkv, D]; the CTA whose
-    // tile holds a sequence's newest position writes the row into the cache and into its tile
+    // fused append (rotating kernels only): this step's K and V projections [B, Hkv, D], 16-byte aligned
+    // (the masked rows of the sequence's last tile are filled from them with 16-byte asynchronous copies);
+    // the CTA whose tile holds a sequence's newest position writes the row into the cache and into its tile
     const __half* k_new; const __half* v_new;
 };
 
@@ -82,11 +94,9 @@ __device__ __forceinline__ unsigned long long trace_globaltimer() {
 }
 #define VTEB_TR(ctx, slot) do { if ((ctx).base != nullptr && (threadIdx.x & 31) == 0) (ctx).base[slot] = (unsigned long long)clock64(); } while (0)
 #define VTEB_TR_GT(ctx, slot) do { if ((ctx).base != nullptr && (threadIdx.x & 31) == 0) (ctx).base[slot] = trace_globaltimer(); } while (0)
-#define VTEB_TR_ADD(ctx, slot, v) do { if ((ctx).base != nullptr && (threadIdx.x & 31) == 0) (ctx).base[slot] += (unsigned long long)(v); } while (0)
 #else
 #define VTEB_TR(ctx, slot) do { } while (0)
 #define VTEB_TR_GT(ctx, slot) do { } while (0)
-#define VTEB_TR_ADD(ctx, slot, v) do { } while (0)
 #endif
 
 // Stores four (or two) normalised output values; out_kind 1 = fp16, 2 = fp32.
@@ -188,6 +198,10 @@ __device__ __forceinline__ void copy_rows_async(const unsigned char* src, const 
 // layer's launch.  HBM then stays busy while this launch drains its tail and the
 // combine runs, and the next launch starts from L2.  Every byte is still read
 // from HBM once per step.  Requests are 8 KB each, spread over the lanes.
+// Its place matters: issued right after the loader's last tile and its (fruitless) ticket
+// draw it is worth 0.35 us per 32k-context layer (1.2 us per launch when split launches run back to
+// back); issued one atomic round trip earlier it is worth 0.07 us less, and held back until the
+// consumers have released the last tile it costs 1.2 us.
 // The prefetch only pays while a whole layer's K and V stay in L2 until the next launch reads
 // them: above this many bytes per tensor (the grid's total) it is skipped.  Measured at one
 // million positions (0.5 GB per tensor): prefetching cost 15 % of the throughput.
@@ -716,6 +730,77 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
             merge_parity ^= 1u;
             VTEB_TR(tr, 6);
 
+            if constexpr (VTEB_MERGE_PAIRS == 2 && D <= 128) {
+            // Two (KV head, query row) pairs per warp pass, one per half-warp: a lane derives its pair's
+            // weights from broadcast reads and merges D / 16 consecutive columns.  With 12 query heads and six
+            // warps the CTA's merge is one pass instead of two.
+            const bool empty = (flags & kTileEmpty) != 0;
+            const int heads_item = plan.hg * group;                    // query heads of this item
+            const long long stat0 = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * heads_item) * a.max_chunks + item_c;
+            const bool write_o = !empty || (a.flags & kFlagWriteEmptyO);
+            for (int hq0 = 2 * warp; hq0 < heads_item; hq0 += 2 * plan.active_warps) {
+                const int hq = hq0 + (lane >> 4), l16 = lane & 15;
+                const bool pair_ok = hq < heads_item;
+                const int hqc = pair_ok ? hq : hq0;                     // an idle half-warp reads the first pair's rows
+                const int kvh = hqc / group, row = hqc - kvh * group;
+                const float* src0 = merge + ((size_t)kvh * group + row) * pitch;        // warp (sub 0, half 0, kvh)
+                const size_t hstride = (size_t)plan.hg * group * pitch;                  // same sub, next column half
+                const size_t wstride = hstride * DS;                                     // next sub of the same head
+                constexpr int FPL = D / 16, NV = FPL / 4;                                // floats / float4s per lane
+                const int col0 = l16 * FPL;
+                float mw[CW], lw[CW];
+                float4 ow[CW][NV];
+#pragma unroll
+                for (int w = 0; w < CW; ++w) {
+                    const bool on = w < plan.wph;
+                    const float* src = src0 + (on ? w : 0) * wstride;
+                    mw[w] = on ? src[D + 4] : kNeutralM;
+                    lw[w] = on ? src[D + 5] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        const int col = col0 + 4 * i;                  // lies in column half col / DW, written by that half's warp
+                        ow[w][i] = on ? *reinterpret_cast<const float4*>(src + (col / DW) * hstride + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                float mm = kNeutralM;
+#pragma unroll
+                for (int w = 0; w < CW; ++w) mm = fmaxf(mm, mw[w]);
+                float ll = 0.f;
+                float4 acc[NV];
+#pragma unroll
+                for (int i = 0; i < NV; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < CW; ++w) {
+                    const float wt = fast_exp2(mw[w] - mm);       // absent warps: exp2(-1e30 - mm) = 0 (or 1 * zeros)
+                    ll = fmaf(lw[w], wt, ll);
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        acc[i].x = fmaf(ow[w][i].x, wt, acc[i].x); acc[i].y = fmaf(ow[w][i].y, wt, acc[i].y);
+                        acc[i].z = fmaf(ow[w][i].z, wt, acc[i].z); acc[i].w = fmaf(ow[w][i].w, wt, acc[i].w);
+                    }
+                }
+                if (!pair_ok) continue;
+                if (a.flags & kFlagDirectOutput) {
+                    const long long orow = (long long)item_b * a.num_q_heads + (long long)item_hgroup * heads_item + hq;
+                    const float inv = 1.f / fmaxf(ll, 1e-20f);
+#pragma unroll
+                    for (int i = 0; i < NV; ++i)
+                        store_out4(a.output, a.out_kind, orow * D + col0 + 4 * i,
+                                   make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv));
+                    continue;
+                }
+                const long long stat = stat0 + (long long)hq * a.max_chunks;
+                if (write_o) {
+#pragma unroll
+                    for (int i = 0; i < NV; ++i)
+                        *reinterpret_cast<float4*>(a.partial_o + stat * D + col0 + 4 * i) = acc[i];
+                }
+                if (l16 == 0) {
+                    a.partial_m[stat] = empty ? kNeutralM : mm * kLn2;
+                    a.partial_l[stat] = empty ? 0.f : ll;
+                }
+            }
+            } else {
             // One (KV head, query row) pair per warp pass: all lanes derive the pair's
             // weights from broadcast reads, then each lane merges its float4 columns.
             const bool empty = (flags & kTileEmpty) != 0;
@@ -780,6 +865,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                     a.partial_m[stat] = empty ? kNeutralM : mm * kLn2;
                     a.partial_l[stat] = empty ? 0.f : ll;
                 }
+            }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(merge_bar0 + 8);
