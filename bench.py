@@ -60,7 +60,7 @@ MIN_TRIAL_MS = 50.0
 # (workload, compact CTA shape).  A rebuilt kernel has another hash and reports traffic null until it
 # is captured again.
 NCU_TRAFFIC_BYTES: dict[str, dict[tuple[str, bool], int]] = {
-    "278a70666a1f0948": {("c2", True): 33623211},      # 33.62 MB read, <= 768 B written back: three launches of the 8-layer case
+    "14b2c1dd0c012e64": {("c2", True): 33621931},      # 33.62 MB read, nothing written back (partials stay in L2): three launches of the 8-layer case
 }
 
 
@@ -284,7 +284,8 @@ def measure_sequences(args, rt, rdzv, rank, world, workload, n_layers, n_kv, ste
     local = replace(cfg, batch=len(mine))
     ex = DecodeAttentionExecutor(rt, CodegenEngine(), metadata(cfg), local.batch, cfg.max_seq, n_layers,
                                  n_kv_buffers=n_kv, output_f32=True, variant=args.variant,
-                                 num_splits=args.splits or None, min_chunk=None if args.min_chunk < 0 else args.min_chunk)
+                                 num_splits=args.splits or None, min_chunk=None if args.min_chunk < 0 else args.min_chunk,
+                                 balanced=False if args.no_balanced else (True if args.force_balanced else None))
     try:
         for buf in range(n_kv):
             _fill_sequences(rt, ex, cfg, buf, mine)
@@ -320,6 +321,7 @@ def measure_sequences(args, rt, rdzv, rank, world, workload, n_layers, n_kv, ste
             "ms_per_step_min_max": [t["min_ms"], t["max_ms"]], "replays_per_trial": t["replays_per_trial"],
             "positions_per_gpu_max_over_mean": max(loads) / (sum(loads) / len(loads)),
             "splits": ex.dispatcher.max_chunks, "min_chunk": ex.dispatcher.min_chunk,
+            "positions_to_ctas": "equal shares of all cached positions" if ex.dispatcher.balanced else "work queue of splits",
             "kernels": "fast, compact CTAs" if ex.dispatcher.compact else "fast, full CTAs",
             "parity": {"against": "CPU oracle, layer 0, longest and shortest sequence of every rank", "max_abs": max_abs,
                        "rel_l2": rel, "within_tolerance": bool(max_abs <= 2e-3 and rel <= 1e-2)},
@@ -544,7 +546,8 @@ def run_ours(args, rank, world, local_rank):
                                  programmatic=not args.no_pdl, compat=args.compat,
                                  prefetch_next_layer=not args.no_prefetch,
                                  fused_combine=args.fuse, variant=args.variant, rope=args.rope,
-                                 rope_theta=cfg.rope_theta or 1e6, tensor_maps=not args.no_tma)
+                                 rope_theta=cfg.rope_theta or 1e6, tensor_maps=not args.no_tma,
+                                 balanced=False if args.no_balanced else (True if args.force_balanced else None))
     # ---- inputs: seeded host generation when it is cheap, device-side fill otherwise
     host_layers = {}
     q_all = np.zeros((n_layers, cfg.batch, cfg.num_q_heads, cfg.head_dim), dtype=np.float16)
@@ -786,6 +789,9 @@ def main():
     ap.add_argument("--kv-buffers", type=int, default=0, help="distinct KV caches to cycle through")
     ap.add_argument("--splits", type=int, default=0, help="split count (0 = dispatcher's choice)")
     ap.add_argument("--min-chunk", type=int, default=-1, help="minimum positions per split (-1 = dispatcher's choice)")
+    ap.add_argument("--force-balanced", action="store_true", help="equal shares per CTA even with --splits given")
+    ap.add_argument("--no-balanced", action="store_true",
+                    help="several sequences: splits from a work queue instead of equal shares of all positions per CTA")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     ap.add_argument("--partition", default="", choices=["", "replicas", "sequences", "kv-range"],
                     help="what the line's own value measures with N > 1: replicas (each rank its own copy of the workload, weak; "

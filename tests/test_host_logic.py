@@ -480,3 +480,35 @@ def test_every_kernel_of_the_signature_table_is_in_the_cubin():
 
 def test_oom_error_is_a_safety_error():
     assert issubclass(MemoryGuardianOOMError, CudaSafetyError)
+
+
+def test_balanced_partition_restatement_invariants():
+    """Every position of every (sequence, head group) lies in exactly one piece, pieces of a pair get
+    consecutive split indices from 0, no pair exceeds its splits, and shares differ by a tile at most
+    unless one long sequence forces larger shares."""
+    from vte_b200.core.split_kv_attention import balanced_pieces, balanced_split_count
+    rng = np.random.default_rng(5)
+    for batch, n_hg, lo, hi, tile in ((64, 1, 1024, 16384, 32), (16, 2, 2048, 65536, 32), (8, 1, 1024, 16384, 32),
+                                      (2, 2, 2048, 65536, 64), (3, 4, 1, 40, 16), (5, 1, 1, 3, 64)):
+        lengths = rng.integers(lo, hi + 1, size=batch)
+        C = balanced_split_count(148, batch, n_hg)
+        pieces = balanced_pieces(lengths, n_hg, 148, C, tile)
+        assert len(pieces) == 148
+        cover = {}
+        for cta in pieces:
+            for (b, h, c, a, e) in cta:
+                assert 0 <= c < C and 0 <= a < e <= lengths[b]
+                cover.setdefault((b, h), []).append((c, a, e))
+        assert len(cover) == batch * n_hg
+        for (b, h), lst in cover.items():
+            lst.sort()
+            assert [c for c, _, _ in lst] == list(range(len(lst)))
+            assert lst[0][1] == 0 and lst[-1][2] == lengths[b]
+            assert all(lst[i][2] == lst[i + 1][1] for i in range(len(lst) - 1))
+        sizes = [sum(e - a for (_, _, _, a, e) in cta) for cta in pieces]
+        busy = [s for s in sizes if s]
+        assert max(busy) - min(busy[:-1] or busy) <= tile or max(lengths) * n_hg * 148 > (C - 1) * sum(lengths) * n_hg
+    # one long sequence among short ones: shares grow so that it still fits its splits
+    pieces = balanced_pieces([100000, 10, 10, 10], 1, 148, 8, 32)
+    assert max(c for cta in pieces for (_, _, c, _, _) in cta) <= 7
+    assert sum(1 for cta in pieces if cta) < 148

@@ -119,7 +119,8 @@ def test_fixed_chunk_mode_reproduces_reference_chunking(cuda_runtime, codegen):
         assert_parity(out, ref, tight=5e-5)
 
 
-@pytest.mark.parametrize("shape", [(12, 2, 128), (32, 8, 64), (8, 2, 256)], ids=["q12kv2d128", "q32kv8d64", "q8kv2d256"])
+@pytest.mark.parametrize("shape", [(12, 2, 128), (32, 8, 64), (8, 2, 256), (28, 4, 128), (12, 4, 128)],
+                         ids=["q12kv2d128", "q32kv8d64", "q8kv2d256", "q28kv4d128", "q12kv4d128"])
 def test_every_context_length_up_to_130(cuda_runtime, codegen, shape):
     """Context lengths 1..130 cross every 16-position block and tile boundary and
     leave most splits empty; one captured graph is replayed with new offsets."""
@@ -165,11 +166,51 @@ def test_ragged_batch_matches_oracle(cuda_runtime, codegen):
     cfg = DecodeConfig("c3_small", 3, 16, 32, 8, 64, 100, 4096, 1)
     q, k, v, off = make_layer_inputs(cfg, 0)
     ref = orc.decode_attention(q, k, v, off)
-    out, _, C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off)
+    out, _, C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, balanced=False)
     assert C == 8                  # 512-position work items, the smallest the dispatcher aims at
     assert_parity(out, ref, tight=5e-5)
     out2, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, num_splits=64, min_chunk=64)
     assert_parity(out2, ref, tight=5e-5)
+
+
+@pytest.mark.parametrize("shape", [(16, 32, 8, 64, 100, 4096), (5, 12, 2, 128, 1, 3000), (6, 8, 2, 256, 40, 2500),
+                                   (3, 28, 4, 128, 700, 9000), (2, 8, 8, 128, 1, 129)],
+                         ids=["d64x16", "d128x5", "d256x6", "d128g7x3", "d128mha_short"])
+def test_balanced_partition_matches_oracle(cuda_runtime, codegen, shape):
+    """Several sequences, no split count given: every CTA takes an equal share of all cached positions
+    and a sequence is cut wherever a share ends.  The output, and the partial buffers reduced by the
+    oracle's combine, must match the oracle; splits past a pair's last piece must read as empty; the
+    host restatement of the cuts must agree with which splits the kernel filled."""
+    from vte_b200.core.split_kv_attention import balanced_pieces
+    B, Hq, Hkv, D, lo, hi = shape
+    cfg = DecodeConfig("balanced", 31, B, Hq, Hkv, D, lo, hi, 1)
+    q, k, v, off = make_layer_inputs(cfg, 0)
+    ref = orc.decode_attention(q, k, v, off)
+    for kw in ({}, {"strict_empty_splits": True}, {"num_splits": 3, "balanced": True}):
+        ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 1, **kw)
+        try:
+            d = ex.dispatcher
+            assert d.balanced and d.max_chunks >= 2
+            ex.upload_layer(0, q, k, v)
+            for _ in range(2):                       # replayed: nothing is left over from the first step
+                out = ex.execute_decode_batch(off)[0]
+                assert_parity(out, ref, tight=5e-5)
+            pm, pl, po = ex.read_partials()
+            assert_parity(orc.split_kv_reduce(pm, pl, po), ref, tight=5e-5)
+            plan = d._plan
+            pieces = balanced_pieces(off + 1, plan.n_hgroups, cuda_runtime.get_num_cus(), d.max_chunks, plan.tile)
+            live = np.zeros((B, Hq, d.max_chunks), dtype=bool)
+            heads_pair = Hq // plan.n_hgroups
+            for cta in pieces:
+                for (b, h, c, a, e) in cta:
+                    assert 0 <= c < d.max_chunks and e > a
+                    live[b, h * heads_pair:(h + 1) * heads_pair, c] = True
+            assert np.all(pl[live] > 0)
+            assert np.all(pm[~live] == np.float32(-1e30)) and np.all(pl[~live] == 0)
+            if kw.get("strict_empty_splits"):
+                assert np.all(po[~live] == 0)
+        finally:
+            ex.cleanup()
 
 
 @pytest.mark.parametrize("shape", [(16, 32, 8, 64), (3, 12, 2, 128), (4, 8, 2, 256)], ids=["d64", "d128", "d256"])

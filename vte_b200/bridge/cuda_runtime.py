@@ -48,6 +48,7 @@ ATTN_WRITE_EMPTY_O = 2
 ATTN_PROGRAMMATIC = 4
 ATTN_COMPACT = 16
 ATTN_NO_TENSOR_MAPS = 32
+ATTN_BALANCED = 64
 
 ERR_DEVICE_STATUS = -6
 

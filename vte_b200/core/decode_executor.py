@@ -38,7 +38,8 @@ class DecodeAttentionExecutor:
                  strict_empty_splits: bool = False, allocator: Optional[SlabAllocator] = None,
                  emit_state: bool = False, per_layer_hook=None, prefetch_next_layer: bool = True,
                  fused_combine: Optional[bool] = None, variant: str = "auto", rope: str = "off",
-                 rope_theta: float = 1e6, tensor_maps: bool = True, fuse_append: bool = False):
+                 rope_theta: float = 1e6, tensor_maps: bool = True, fuse_append: bool = False,
+                 balanced: Optional[bool] = None):
         self.hip = hip
         # rope: "off" = Q and K arrive rotated; "separate" = the reference's standalone rotation
         # launch runs before the append (rotating the projections in place); "fused" = the append
@@ -101,7 +102,7 @@ class DecodeAttentionExecutor:
             output_f32=self.output_f32, strict_empty_splits=strict_empty_splits, emit_state=self.emit_state,
             prefetch_next_layer=prefetch_next_layer, fused_combine=fused_combine, variant=variant,
             fuse_rope=rope in ("fused", "fused-append"), fuse_append=(rope == "fused-append" or fuse_append), tensor_maps=tensor_maps,
-            work_ptr=self.out_all.ptr + self._out_tail)
+            work_ptr=self.out_all.ptr + self._out_tail, balanced=balanced)
 
         self.k_cache = [A(self.kv_bytes, f"kv_cache.k.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]
         self.v_cache = [A(self.kv_bytes, f"kv_cache.v.{i}", MemoryRegion.KV_CACHE) for i in range(self.n_kv)]

@@ -34,6 +34,7 @@ FLAG_WRITE_EMPTY_O = 1
 FLAG_DIRECT_OUTPUT = 2
 FLAG_TENSOR_MAPS = 4
 FLAG_PREFETCH_Q = 8
+FLAG_BALANCED = 16
 COMPACT_MAX_CONTEXT = 262144      # one sequence up to this long: the compact CTA shape (launches of tens of microseconds)
 UNSPLIT_MAX_CONTEXT = 128         # below this, one CTA per (sequence, head group) finishes before a combine could launch
 
@@ -63,6 +64,48 @@ def choose_chunk_positions(num_sms: int, batch: int, n_hgroups: int, context_len
     return chunk
 
 
+def balanced_split_count(num_sms: int, batch: int, n_hgroups: int) -> int:
+    """Splits reserved per (sequence, head group) for the balanced partition.  A pair of S positions is
+    cut into at most ceil(S / share) + 1 pieces, where share = all positions / num_sms; with equal
+    lengths that is num_sms / pairs + 1.  Eight times that (one pair may be eight times the mean length
+    before the kernel has to enlarge the shares and leave CTAs idle), kept within the 64 splits of the
+    one-warp-per-row combine, whose cost follows the splits in use and not the splits reserved; with so
+    few pairs that 64 cannot hold 2.5 times the mean, that many and the wide combine."""
+    pairs = max(1, batch * n_hgroups)
+    want = math.ceil(8 * num_sms / pairs) + 1
+    if want <= 64:
+        return max(8, want)
+    need = min(num_sms, math.ceil(2.5 * num_sms / pairs)) + 1
+    return 64 if need <= 64 else min(MAX_SPLITS, need)
+
+
+def balanced_pieces(lengths, n_hgroups: int, n_ctas: int, max_chunks: int, tile: int):
+    """Host restatement of the split kernel's balanced partition (split_kv_fast.cuh, BalancedShare):
+    the list, per CTA, of its pieces (sequence, head group, split index, first position, end position).
+    Used by tests and for sizing; the kernel derives the same cuts from the offsets on the device."""
+    lengths = [int(x) for x in lengths]
+    total = sum(lengths) * n_hgroups
+    per = -(-total // n_ctas)
+    slots = max(1, max_chunks - 1)
+    per = max(per, -(-max(lengths) // slots), 1)
+    per = -(-per // tile) * tile
+    firsts, acc = [], 0
+    for s in lengths:
+        for h in range(n_hgroups):
+            firsts.append((acc, s, len(firsts) // n_hgroups, h))
+            acc += s
+    out = []
+    for cta in range(n_ctas):
+        lo, hi = min(cta * per, total), min((cta + 1) * per, total)
+        mine = []
+        for first, s, b, h in firsts:
+            a, e = max(lo, first), min(hi, first + s)
+            if e > a:
+                mine.append((b, h, a // per - first // per, a - first, e - first))
+        out.append(mine)
+    return out
+
+
 def choose_split_count(num_sms: int, batch: int, n_hgroups: int, context_length: int) -> int:
     """Split count when the caller does not fix one.
 
@@ -88,7 +131,8 @@ class SplitKVAttentionDispatcher:
                  compat: bool | None = None, min_chunk: int | None = None, output_f32: bool = False,
                  strict_empty_splits: bool = False, emit_state: bool = False, prefetch_next_layer: bool = True,
                  fused_combine: bool | None = None, variant: str = "auto", fuse_rope: bool = False,
-                 tensor_maps: bool = True, work_ptr: int | None = None, fuse_append: bool = False):
+                 tensor_maps: bool = True, work_ptr: int | None = None, fuse_append: bool = False,
+                 balanced: bool | None = None):
         self.hip = hip
         self.codegen = codegen
         self.metadata = metadata or {}
@@ -151,20 +195,37 @@ class SplitKVAttentionDispatcher:
                 raise CudaSafetyError(f"fixed_chunk_size must be positive, got {fixed_chunk_size}")
             self.max_chunks = max(1, math.ceil(self.context_length / self.chunk_size))
             self.fixed_chunk = True
+            self.balanced = False
+            if balanced:
+                raise CudaSafetyError("the balanced partition and a fixed chunk size exclude each other")
         else:
             self.fixed_chunk = False
             n_hg = self._plan.n_hgroups if (self._plan is not None and self._plan.ok) else self.num_kv_heads
+            # balanced: every CTA takes an equal share of all cached positions instead of drawing
+            # fixed-size splits from a work queue (split_kv_fast.cuh, BalancedShare).  Chosen when several
+            # sequences share the GPU and the caller fixed neither the split count nor a minimum split.
+            fast = (not self.compat) and self._plan is not None and self._plan.ok
+            auto_count = not num_splits
+            self.balanced = fast and not self.fused_combine and not self.compact and (
+                (balanced is None and auto_count and min_chunk is None and self.batch_size > 1
+                 and self.context_length > UNSPLIT_MAX_CONTEXT) or bool(balanced))
+            if self.balanced and self.batch_size * n_hg < 2:
+                self.balanced = False
             if num_splits:
                 self.max_chunks = int(num_splits)
+            elif self.balanced:
+                self.max_chunks = balanced_split_count(num_cus, self.batch_size, n_hg)
             else:
                 self.max_chunks = choose_split_count(num_cus, self.batch_size, n_hg, self.context_length)
+            if self.balanced and self.max_chunks < 2:
+                raise CudaSafetyError("the balanced partition needs at least two splits")
             if not (1 <= self.max_chunks <= 65535):
                 raise CudaSafetyError(f"split count {self.max_chunks} outside 1..65535")
             self.chunk_size = 0
         if min_chunk is None:
             n_hg = self._plan.n_hgroups if (self._plan is not None and self._plan.ok) else self.num_kv_heads
             min_chunk = (choose_chunk_positions(num_cus, self.batch_size, n_hg, self.context_length)
-                         if (self.batch_size > 1 and not self.fixed_chunk) else 0)
+                         if (self.batch_size > 1 and not self.fixed_chunk and not self.balanced) else 0)
         self.min_chunk = int(min_chunk)
 
         # fuse_rope: q_name / k_name are the UN-rotated projections; the append launch rotates the K
@@ -405,8 +466,10 @@ class SplitKVAttentionDispatcher:
 
         plan = self._plan
         items = batch * plan.n_hgroups * C
-        n_ctas = max(1, min(items, self.num_sms))
+        n_ctas = self.num_sms if self.balanced else max(1, min(items, self.num_sms))
         flags = FLAG_WRITE_EMPTY_O if self.strict_empty_splits else 0
+        if self.balanced:
+            flags |= FLAG_BALANCED
         # Under programmatic dependent launch the split CTAs start while the launch before them still runs:
         # the loader asks L2 for the Q rows (a hint only, no data reaches the SM) so that the consumers'
         # fetch after the dependency wait does not go to DRAM.  With plain stream order the wait returns at

@@ -13,7 +13,15 @@
 
 #include "vteb_common.cuh"
 
+#ifndef VTEB_LAZY_MAX
+#define VTEB_LAZY_MAX 8   // 0: the reference maximum follows every block's maximum
+#endif
+
 namespace vteb {
+
+// Where a warp's exchange row keeps the row's true maximum: a slot of its own under the lazy
+// maximum, the reference maximum's slot (D + 4) otherwise.
+constexpr int kMergeTrueMax = (VTEB_LAZY_MAX > 0) ? 6 : 4;
 
 // Scores of one block: sn[0] positions 0..7, sn[1] positions 8..15 (raw dot products, unscaled),
 // thread (g = lane / 4, t = lane % 4) holds query row g, positions 2t, 2t+1 of each half.
@@ -61,14 +69,26 @@ struct ConsumerState {
     float o[NT][2];
     float o_lo[LOACC ? NT : 1][2];
     float m, l;
+    float mt;   // lazy maximum only: this thread's largest score so far (m then lags behind the row's true maximum)
     __device__ __forceinline__ void reset() {
-        m = kNeutralM; l = 0.f;
+        m = kNeutralM; l = 0.f; mt = kNeutralM;
 #pragma unroll
         for (int n = 0; n < NT; ++n) { o[n][0] = 0.f; o[n][1] = 0.f; }
         if constexpr (LOACC) {
 #pragma unroll
             for (int n = 0; n < NT; ++n) { o_lo[n][0] = 0.f; o_lo[n][1] = 0.f; }
         }
+    }
+    // The row's true maximum (quad-wide); equals m unless the maximum is lazy.
+    __device__ __forceinline__ float true_max() const {
+#if VTEB_LAZY_MAX > 0
+        float v = mt;
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        return v;
+#else
+        return m;
+#endif
     }
     __device__ __forceinline__ void fold_lo() {
         if constexpr (LOACC) {
@@ -108,6 +128,27 @@ __device__ __forceinline__ void softmax_pv(ConsumerState<NT, LOACC>& st, const f
             s[n][j] = valid ? sraw[n][j] * scale2 : kNeutralM;
             mx = fmaxf(mx, s[n][j]);
         }
+#if VTEB_LAZY_MAX > 0
+    // The reference maximum m moves only when some score of the warp exceeds it by more than
+    // VTEB_LAZY_MAX (log2 units): probabilities then reach 2^VTEB_LAZY_MAX at most, and the two
+    // shuffles, the correction factor and the rescaling leave the chain of nearly every block.
+    st.mt = fmaxf(st.mt, mx);
+    if (__any_sync(0xffffffffu, mx > st.m + (float)VTEB_LAZY_MAX)) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_up = fmaxf(st.m, mx);
+        const float corr = fast_exp2(st.m - m_up);
+        st.l *= corr;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { st.o[n][0] *= corr; st.o[n][1] *= corr; }
+        if constexpr (LOACC) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) { st.o_lo[n][0] *= corr; st.o_lo[n][1] *= corr; }
+        }
+        st.m = m_up;
+    }
+    const float m_new = st.m;
+#else
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(st.m, mx);
@@ -122,6 +163,7 @@ __device__ __forceinline__ void softmax_pv(ConsumerState<NT, LOACC>& st, const f
         }
     }
     st.m = m_new;
+#endif
     float p[2][2];
 #pragma unroll
     for (int n = 0; n < 2; ++n)
@@ -165,6 +207,144 @@ __device__ __forceinline__ void softmax_pv(ConsumerState<NT, LOACC>& st, const f
                 st.o[n][0] += e0; st.o[n][1] += e1; st.o[n + 1][0] += f0; st.o[n + 1][1] += f1;
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Transposed form of the same block: positions are the M dimension of both products.
+//   S^T (16 positions x 8 heads) = K (A operand, all 16 rows used) * Q^T (B operand),
+//   O^T (16 columns x 8 heads)  += V^T (A operand) * P^T (B operand, fp16 high part, then low part).
+// Against the form above: 8 + 16 instead of 16 + 16 mma.sync per block, no additions of a
+// low-part product, and four movmatrix transposes that turn the S^T accumulator fragment into
+// the B fragments of P^T.  The ldmatrix loads are the same ones, taken in another register order.
+// Thread (g = lane / 4, t = lane % 4) holds heads 2t and 2t+1: scores of positions g and g+8,
+// output columns 16*mt + g and + 8 of every 16-column tile mt.
+
+__device__ __forceinline__ void mma_full(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 8x8 transpose of 16-bit elements across the warp: lane (g, t) gives row g, columns 2t, 2t+1
+// and receives row g, columns 2t, 2t+1 of the transposed matrix.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
+template <int MT>
+struct ConsumerStateT {
+    float o[MT][4];       // tile mt: (column 16mt+g, head 2t), (same, head 2t+1), (column 16mt+g+8, head 2t), (same, head 2t+1)
+    float m[2], l[2];     // reference maximum (log2 domain) and this thread's part of the sum, heads 2t and 2t+1
+    float mt[2];          // this thread's largest score per head (lazy maximum only)
+    __device__ __forceinline__ void reset() {
+        m[0] = m[1] = kNeutralM; l[0] = l[1] = 0.f; mt[0] = mt[1] = kNeutralM;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    }
+};
+
+// Maximum / sum over the eight lanes that share t (the positions of a head).
+__device__ __forceinline__ float max_over_g(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+}
+__device__ __forceinline__ float sum_over_g(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    return v + __shfl_xor_sync(0xffffffffu, v, 16);
+}
+
+// Raw scores of one block: s[0] (position g, head 2t), s[1] (g, 2t+1), s[2] (g+8, 2t), s[3] (g+8, 2t+1).
+template <int D>
+__device__ __forceinline__ void qk_block_t(const uint32_t* __restrict__ q_frag, uint32_t kaddr, int blk_bytes, float (&s)[4]) {
+    constexpr int KS = D / 16;
+    float acc[2][4];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) { acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f; }
+    constexpr int KC = KS < 8 ? KS : 8;
+#pragma unroll
+    for (int kc = 0; kc < KS; kc += KC) {
+        uint32_t kf[KC][4];
+#pragma unroll
+        for (int i = 0; i < KC; ++i)
+            ldmatrix_x4((kaddr ^ (((kc + i) & 3) << 5)) + ((kc + i) >> 2) * blk_bytes, kf[i][0], kf[i][1], kf[i][2], kf[i][3]);
+#pragma unroll
+        for (int i = 0; i < KC; ++i) {
+            const int ks = kc + i;
+            // kf: (positions 0-7, k 0-7), (0-7, 8-15), (8-15, 0-7), (8-15, 8-15); the A operand wants rows before columns
+            mma_full(acc[ks & 1], kf[i][0], kf[i][2], kf[i][1], kf[i][3], q_frag[(2 * ks) * 32], q_frag[(2 * ks + 1) * 32]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = acc[0][i] + acc[1][i];
+}
+
+template <int MT>
+__device__ __forceinline__ void softmax_pv_t(ConsumerStateT<MT>& st, const float (&sraw)[4], uint32_t vaddr, int blk_bytes,
+                                             int left, float scale2, int g) {
+    constexpr int VC = (MT >= 4) ? 4 : MT;       // ldmatrix.x4.trans per chunk (4 = 64 output columns)
+    constexpr int NVC = MT / VC;
+    uint32_t vf[2][VC][4];
+#pragma unroll
+    for (int i = 0; i < VC; ++i) ldmatrix_x4_trans(vaddr ^ (i << 5), vf[0][i][0], vf[0][i][1], vf[0][i][2], vf[0][i][3]);
+    const bool valid[2] = {g < left, g + 8 < left};
+    float s[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = valid[i >> 1] ? sraw[i] * scale2 : kNeutralM;
+    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#if VTEB_LAZY_MAX > 0
+    st.mt[0] = fmaxf(st.mt[0], mx[0]);
+    st.mt[1] = fmaxf(st.mt[1], mx[1]);
+    const bool move = __any_sync(0xffffffffu, (mx[0] > st.m[0] + (float)VTEB_LAZY_MAX) | (mx[1] > st.m[1] + (float)VTEB_LAZY_MAX));
+#else
+    const bool move = true;
+#endif
+    if (move) {
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float m_up = fmaxf(st.m[h], max_over_g(mx[h]));
+            corr[h] = fast_exp2(st.m[h] - m_up);
+            st.l[h] *= corr[h];
+            st.m[h] = m_up;
+        }
+#pragma unroll
+        for (int i = 0; i < MT; ++i) { st.o[i][0] *= corr[0]; st.o[i][1] *= corr[1]; st.o[i][2] *= corr[0]; st.o[i][3] *= corr[1]; }
+    }
+    float p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = valid[i >> 1] ? fast_exp2(s[i] - st.m[i & 1]) : 0.f;
+    st.l[0] += p[0] + p[2];
+    st.l[1] += p[1] + p[3];
+    // P = P_hi + P_lo, both fp16; rows of the 8x8 matrices are positions, columns heads: transpose into B fragments
+    uint32_t bh[2], bl[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const __half2 hi = __floats2half2_rn(p[2 * r], p[2 * r + 1]);
+        const float2 hif = __half22float2(hi);
+        bh[r] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
+        bl[r] = movmatrix_trans(pack_half2(p[2 * r] - hif.x, p[2 * r + 1] - hif.y));
+    }
+#pragma unroll
+    for (int ch = 0; ch < NVC; ++ch) {
+        if (ch + 1 < NVC) {
+#pragma unroll
+            for (int i = 0; i < VC; ++i)
+                ldmatrix_x4_trans((vaddr ^ (i << 5)) + (ch + 1) * blk_bytes, vf[(ch + 1) & 1][i][0], vf[(ch + 1) & 1][i][1],
+                                  vf[(ch + 1) & 1][i][2], vf[(ch + 1) & 1][i][3]);
+        }
+        // vf: (positions 0-7, columns 0-7)^T, (8-15, 0-7)^T, (0-7, 8-15)^T, (8-15, 8-15)^T
+#pragma unroll
+        for (int i = 0; i < VC; ++i)
+            mma_full(st.o[ch * VC + i], vf[ch & 1][i][0], vf[ch & 1][i][2], vf[ch & 1][i][1], vf[ch & 1][i][3], bh[0], bh[1]);
+#pragma unroll
+        for (int i = 0; i < VC; ++i)
+            mma_full(st.o[ch * VC + i], vf[ch & 1][i][0], vf[ch & 1][i][2], vf[ch & 1][i][1], vf[ch & 1][i][3], bl[0], bl[1]);
     }
 }
 

@@ -78,6 +78,7 @@ struct FastArgs {
 constexpr int kFlagWriteEmptyO = 1;   // also zero partial_o of empty splits (reference semantics)
 constexpr int kFlagDirectOutput = 2;  // max_chunks == 1: normalise and store the attention output here, no partials
 constexpr int kFlagTensorMaps = 4;    // tmap_k / tmap_v are valid: whole tiles are fetched with tensor-map copies
+constexpr int kFlagBalanced = 16;     // several sequences: every CTA takes an equal share of all cached positions (see BalancedShare), no work queue
 constexpr int kFlagPrefetchQ = 8;     // ask L2 for an item's Q rows ahead of their use (the first item's before the dependency wait); a hint, no data is read
 
 // ---- optional timeline trace (compiled in with -DVTEB_TRACE=1, used by vte_b200/trace_timeline.py) ----
@@ -257,6 +258,84 @@ __device__ __forceinline__ ItemGeometry decode_item(const FastArgs& a, const Fas
     return g;
 }
 
+// ---- balanced partition ---------------------------------------------------------------------
+// Several sequences on one GPU (kFlagBalanced): the cached positions of all (sequence, head group)
+// pairs, laid end to end in the order pair = sequence * n_hgroups + head group, are cut into
+// gridDim.x equal shares, one per CTA; a CTA's work items are the pieces of pairs inside its share.
+// Every CTA streams the same number of bytes, nothing is drawn from a queue, and the only cost of a
+// ragged batch is one more merge wherever a share crosses the end of a pair.  Piece k of a pair (in
+// position order) is the pair's split k; the pair's remaining splits are marked empty (the rows are
+// dealt to the CTAs in equal runs).  `per` is raised where needed so that no pair is cut into more than
+// max_chunks pieces (CTAs at the end of the grid then stay idle).
+struct BalancedShare {
+    long long total;   // positions of all pairs
+    int per;           // positions per CTA, a multiple of the tile
+};
+
+__device__ __forceinline__ BalancedShare balanced_share(const FastArgs& a, const FastPlan& plan, int lane) {
+    long long sum = 0;
+    int longest = 0;
+    for (int b0 = 0; b0 < a.batch; b0 += 32) {
+        const int s = (b0 + lane < a.batch) ? a.kv_offsets[b0 + lane] + 1 : 0;
+        sum += s;
+        longest = max(longest, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+    }
+    BalancedShare bs;
+    bs.total = sum * plan.n_hgroups;
+    long long per = (bs.total + gridDim.x - 1) / gridDim.x;
+    const int slots = max(1, a.max_chunks - 1);             // a pair of S positions meets at most ceil(S / per) + 1 shares
+    per = max(per, (long long)((longest + slots - 1) / slots));
+    per = max(per, 1ll);
+    bs.per = (int)((per + plan.tile - 1) / plan.tile) * plan.tile;
+    return bs;
+}
+
+// The piece that starts at position x of the laid-out pairs and ends at `hi` or at its pair's end,
+// whichever comes first (lo <= x < hi <= total).  Warp-cooperative: all lanes call it with the same
+// arguments and get the same answer.  `ends_pair` tells whether the piece is its pair's last.
+__device__ __forceinline__ ItemGeometry balanced_piece(const FastArgs& a, const FastPlan& plan, const BalancedShare& bs,
+                                                       long long x, long long hi, int lane, bool& ends_pair) {
+    ItemGeometry g;
+    g.b = g.hgroup = g.c = g.start = g.end = 0;
+    ends_pair = false;
+    long long base = 0;
+    for (int b0 = 0; b0 < a.batch; b0 += 32) {
+        const int s = (b0 + lane < a.batch) ? a.kv_offsets[b0 + lane] + 1 : 0;
+        const long long mine = (long long)s * plan.n_hgroups;
+        long long incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        const long long first = base + incl - mine;          // where this lane's sequence starts
+        const unsigned hit = __ballot_sync(0xffffffffu, s > 0 && x >= first && x < base + incl);
+        if (hit) {
+            const int src = __ffs(hit) - 1;
+            const int len = __shfl_sync(0xffffffffu, s, src);
+            const long long seq_first = __shfl_sync(0xffffffffu, first, src);
+            const long long off = x - seq_first;
+            g.b = b0 + src;
+            g.hgroup = (int)(off / len);
+            g.start = (int)(off - (long long)g.hgroup * len);
+            const long long pair_first = seq_first + (long long)g.hgroup * len;
+            const long long pair_end = pair_first + len;
+            const long long e = min(hi, pair_end);
+            g.end = g.start + (int)(e - x);
+            g.c = (int)(x / bs.per) - (int)(pair_first / bs.per);
+            ends_pair = (e == pair_end);
+            return g;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    return g;   // not reached for x < total
+}
+
 // Fused append: the newest row of a sequence for the item's head group (`new_row`, hg * D halves,
 // rotated at `pos` unless rope_type < 0 or `rotate` is false) goes to its place in the cache and to
 // row `r` of the tile at `tile_dst` (swizzled layout), four bytes per lane and step.
@@ -305,10 +384,24 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // The first item's geometry needs one global load (the sequence's kv offset): start it
     // before the barrier set-up so its latency is hidden.
-    const int total_items = a.batch * plan.n_hgroups * a.max_chunks;
+    const bool balanced = !kCompact && (a.flags & kFlagBalanced) != 0;   // the compact shape serves one sequence: no such code in it
+    int total_items = a.batch * plan.n_hgroups * a.max_chunks;
     ItemGeometry first_geom;
     first_geom.b = first_geom.hgroup = first_geom.c = first_geom.start = first_geom.end = 0;
-    if ((int)blockIdx.x < total_items) first_geom = decode_item(a, plan, blockIdx.x);
+    BalancedShare share;
+    share.total = 0; share.per = 1;
+    long long share_lo = 0, share_hi = 0;      // this CTA's positions of the laid-out pairs (balanced partition)
+    bool first_ends_pair = false;
+    if (balanced) {
+        share = balanced_share(a, plan, threadIdx.x & 31);
+        share_lo = min((long long)blockIdx.x * share.per, share.total);
+        share_hi = min(share_lo + share.per, share.total);
+        // below, "blockIdx.x < total_items" reads "this CTA has a first item"
+        total_items = (share_hi > share_lo) ? (int)gridDim.x : 0;
+        if (share_hi > share_lo) first_geom = balanced_piece(a, plan, share, share_lo, share_hi, threadIdx.x & 31, first_ends_pair);
+    } else if ((int)blockIdx.x < total_items) {
+        first_geom = decode_item(a, plan, blockIdx.x);
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
@@ -360,11 +453,15 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         uint32_t empty_parity = 0;
         bool dep_done = false;
         int item = blockIdx.x;
+        long long cursor = share_lo;               // balanced partition: where the next piece starts
         bool alive = true;
         while (alive) {
-            const bool stop = item >= total_items;
+            const bool stop = balanced ? (cursor >= share_hi) : (item >= total_items);
             ItemGeometry g = first_geom;
-            if (!stop && item != (int)blockIdx.x) g = decode_item(a, plan, item);
+            if (!stop && item != (int)blockIdx.x) {
+                bool ends_pair;
+                g = balanced ? balanced_piece(a, plan, share, cursor, share_hi, lane, ends_pair) : decode_item(a, plan, item);
+            }
             const int ntiles = stop ? 1 : max(1, (g.end - g.start + plan.tile - 1) / plan.tile);
             if ((a.flags & kFlagPrefetchQ) && !stop && item != (int)blockIdx.x && g.c == 0 && g.end > g.start && lane == 0) {
                 // a later item: the loader runs several tiles ahead of the consumers, so asking L2 for the
@@ -452,6 +549,12 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 stage = (stage + 1 == nstages) ? 0 : stage + 1;
             }
             if (stop || !alive) break;
+            if (balanced) {
+                // the next piece of this CTA's share; `item` only has to differ from blockIdx.x from now on
+                cursor += g.end - g.start;
+                item = -1;
+                continue;
+            }
             // Later items come from the shared ticket, which the previous combine
             // launch reset: it may only be touched once that launch has completed.
             if (!dep_done) { grid_dependency_wait(); dep_done = true; }
@@ -471,6 +574,44 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                   (long long)(g.end - g.start) * pos_stride, lane);
         }
         if (!dep_done) grid_dependency_wait();
+        if (balanced && alive) {
+            // Splits past a pair's last piece hold nothing: mark them empty for the combine, as the
+            // reference's kernel does for chunks past the sequence (flash_attention_split_kv_partial.hip.template:59-69).
+            // The (sequence, query head) rows are dealt to the CTAs in equal runs, whatever their shares hold, so
+            // that no CTA has more than a few rows to mark and one prefix sum of the lengths serves a whole run.  After the dependency wait: the launch before this
+            // one may still have read the partial buffers.
+            const int heads_pair = plan.hg * group;
+            const int rows = a.batch * a.num_q_heads;
+            const int rows_per_cta = (rows + gridDim.x - 1) / gridDim.x;
+            const int row0 = blockIdx.x * rows_per_cta, row1 = min(rows, row0 + rows_per_cta);
+            if (row0 < row1) {
+                int b = row0 / a.num_q_heads;
+                long long before = 0;                                  // positions of the sequences ahead of b
+                for (int b0 = 0; b0 < b; b0 += 32)
+                    before += (b0 + lane < b) ? a.kv_offsets[b0 + lane] + 1 : 0;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+                int len = a.kv_offsets[b] + 1;
+                for (int row = row0; row < row1;) {
+                    if (row >= (b + 1) * a.num_q_heads) { before += len; ++b; len = a.kv_offsets[b] + 1; }
+                    // the rows of one pair share their number of pieces: one pair (or what this run holds of it) per turn
+                    const int hgroup = (row - b * a.num_q_heads) / heads_pair;
+                    const int row_end = min(row1, b * a.num_q_heads + (hgroup + 1) * heads_pair);
+                    const long long pair_first = before * plan.n_hgroups + (long long)hgroup * len;
+                    const int live = (int)((pair_first + len - 1) / share.per) - (int)(pair_first / share.per) + 1;
+                    const int idle = a.max_chunks - live;
+                    for (int i = lane; i < (row_end - row) * idle; i += 32) {
+                        const int r = i / idle;
+                        const long long stat = (long long)(row + r) * a.max_chunks + live + (i - r * idle);
+                        a.partial_m[stat] = kNeutralM;
+                        a.partial_l[stat] = 0.f;
+                        if (a.flags & kFlagWriteEmptyO)
+                            for (int d = 0; d < D; ++d) a.partial_o[stat * D + d] = 0.f;
+                    }
+                    row = row_end;
+                }
+            }
+        }
         VTEB_TR(tr, 5);
         asm volatile("cp.async.wait_all;" ::: "memory");   // own copies have landed before the warp leaves
         VTEB_TR(tr, 8);
@@ -551,7 +692,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
     // ===================================================================== consumers
     // warp = (sub * DS + dhalf) * hg + hh
-    constexpr int DS = (D == 256) ? 2 : 1;              // warps sharing one (head, block), split by output columns
+    // 128-wide heads, and 256-wide heads in the full shape, take the transposed form of the block (consumer_block.cuh); its state is `tt`.
+    constexpr bool kT = (VTEB_TRANSPOSED != 0) && (D == 128 || (D == 256 && !kCompact));
+    constexpr int DS = (D == 256 && !kT) ? 2 : 1;       // warps sharing one (head, block), split by output columns
     const int hh = warp % plan.hg;                      // KV head within the group
     const int dhalf = (warp / plan.hg) % DS;            // which part of the output columns this warp owns
     const int sub = warp / (plan.hg * DS);              // which of the wph interleaved block streams
@@ -589,7 +732,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     };
 
     ConsumerState<NT, kLoAcc> st;
+    ConsumerStateT<D / 16> tt;
     st.reset();
+    tt.reset();
     int stage = 0;
     uint32_t full_parity = 0, merge_parity = 0;
     bool merge_pending = false;           // previous item's readers may still use the exchange area
@@ -642,6 +787,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
         if (flags & kTileFirst) {
             st.reset();
+            tt.reset();
             if (!first_item) load_q(item_b, item_hgroup);
             first_item = false;
         }
@@ -651,9 +797,15 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         for (; next_blk < blk0 + blocks_per_tile; next_blk += plan.wph) {
             const int r0 = (next_blk - blk0) * kBlockPos;
             if (r0 >= nvalid) break;
-            float sn[2][2];
-            qk_block<D, kQkChains>(q_frag, (tile_base + r0 * 128 + k_lane_off) | k_lane_x, blk_bytes, sn);
-            softmax_pv<NT, kLoAcc>(st, sn, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, blk_bytes, nvalid - r0, scale2, t);
+            if constexpr (kT) {
+                float sr[4];
+                qk_block_t<D>(q_frag, (tile_base + r0 * 128 + k_lane_off) | k_lane_x, blk_bytes, sr);
+                softmax_pv_t<D / 16>(tt, sr, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, blk_bytes, nvalid - r0, scale2, g);
+            } else {
+                float sn[2][2];
+                qk_block<D, kQkChains>(q_frag, (tile_base + r0 * 128 + k_lane_off) | k_lane_x, blk_bytes, sn);
+                softmax_pv<NT, kLoAcc>(st, sn, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, blk_bytes, nvalid - r0, scale2, t);
+            }
         }
         if (flags & kTileLast) {
             st.fold_lo();
@@ -671,13 +823,25 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         if (flags & kTileLast) {
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
             // ---- exchange (m, l, o) between the warps of each KV head and store the item
-            const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, 2 unused
-            if (plan.wph == 1) {
+            const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, true maximum, 1 unused
+            if (plan.wph == 1 && !kT) {
                 // One warp per KV head: nothing to merge, the warp stores its own state.
+                // (The transposed form goes through the exchange area here too: its registers hold
+                // one column of eight heads, which no global store takes well.)
                 float l_own = st.l;
                 l_own += __shfl_xor_sync(0xffffffffu, l_own, 1);
                 l_own += __shfl_xor_sync(0xffffffffu, l_own, 2);
                 const bool empty1 = (flags & kTileEmpty) != 0;
+#if VTEB_LAZY_MAX > 0
+                {   // restate (m, l, o) against the row's true maximum, as the partial buffers promise
+                    const float m_true = st.true_max();
+                    const float f = fast_exp2(st.m - m_true);
+                    l_own *= f;
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) { st.o[n][0] *= f; st.o[n][1] *= f; }
+                    st.m = m_true;
+                }
+#endif
                 if (g < group && (a.flags & kFlagDirectOutput)) {
                     // unsplit: this warp holds the whole sequence's state for its rows
                     const long long row = (long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
@@ -711,15 +875,39 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 }
                 merge_parity ^= 2u;
             }
-            float l_quad = st.l;
-            l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 1);
-            l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 2);
-            if (g < group) {
-                float* dst = merge + ((size_t)warp * group + g) * pitch;
+            if constexpr (kT) {
+                // thread (g, t): heads 2t, 2t+1; columns 16*mt + g and + 8.  Rows of the exchange area are per (warp, head).
 #pragma unroll
-                for (int n = 0; n < NT; ++n)
-                    *reinterpret_cast<float2*>(dst + dhalf * DW + n * 8 + 2 * t) = make_float2(st.o[n][0], st.o[n][1]);
-                if (t == 0) { dst[D + 4] = st.m; dst[D + 5] = l_quad; }
+                for (int h = 0; h < 2; ++h) {
+                    const int r = 2 * t + h;
+                    const float l_head = sum_over_g(tt.l[h]);
+#if VTEB_LAZY_MAX > 0
+                    const float m_head = max_over_g(tt.mt[h]);
+#else
+                    const float m_head = tt.m[h];
+#endif
+                    if (r < group) {
+                        float* dst = merge + ((size_t)warp * group + r) * pitch;
+#pragma unroll
+                        for (int mt = 0; mt < D / 16; ++mt) {
+                            dst[mt * 16 + g] = tt.o[mt][h];
+                            dst[mt * 16 + g + 8] = tt.o[mt][2 + h];
+                        }
+                        if (g == 0) { dst[D + 4] = tt.m[h]; dst[D + 5] = l_head; dst[D + kMergeTrueMax] = m_head; }
+                    }
+                }
+            } else {
+                float l_quad = st.l;
+                l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 1);
+                l_quad += __shfl_xor_sync(0xffffffffu, l_quad, 2);
+                const float m_true = st.true_max();
+                if (g < group) {
+                    float* dst = merge + ((size_t)warp * group + g) * pitch;
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+                        *reinterpret_cast<float2*>(dst + dhalf * DW + n * 8 + 2 * t) = make_float2(st.o[n][0], st.o[n][1]);
+                    if (t == 0) { dst[D + 4] = st.m; dst[D + 5] = l_quad; dst[D + kMergeTrueMax] = m_true; }
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(merge_bar0);
@@ -748,7 +936,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 const size_t wstride = hstride * DS;                                     // next sub of the same head
                 constexpr int FPL = D / 16, NV = FPL / 4;                                // floats / float4s per lane
                 const int col0 = l16 * FPL;
-                float mw[CW], lw[CW];
+                float mw[CW], lw[CW];            // reference maximum and sum of each warp's row
                 float4 ow[CW][NV];
 #pragma unroll
                 for (int w = 0; w < CW; ++w) {
@@ -762,9 +950,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         ow[w][i] = on ? *reinterpret_cast<const float4*>(src + (col / DW) * hstride + col) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                 }
-                float mm = kNeutralM;
+                float mm = kNeutralM;   // the rows' true maximum (with a lazy maximum the reference values lag behind it)
 #pragma unroll
-                for (int w = 0; w < CW; ++w) mm = fmaxf(mm, mw[w]);
+                for (int w = 0; w < CW; ++w) mm = fmaxf(mm, (w < plan.wph) ? src0[w * wstride + D + kMergeTrueMax] : kNeutralM);
                 float ll = 0.f;
                 float4 acc[NV];
 #pragma unroll
@@ -814,7 +1002,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                 const size_t wstride = hstride * DS;                                     // next sub of the same head
                 constexpr int NV = (D + 127) / 128;                                      // float4 columns per lane
                 const bool col_ok = (D >= 128) || lane < D / 4;
-                float mw[CW], lw[CW];
+                float mw[CW], lw[CW];            // reference maximum and sum of each warp's row
                 float4 ow[CW][NV];
 #pragma unroll
                 for (int w = 0; w < CW; ++w) {
@@ -827,9 +1015,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         ow[w][i] = (on && col_ok) ? *reinterpret_cast<const float4*>(src + ((i * 128) / DW) * hstride + i * 128 + lane * 4)
                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                float mm = kNeutralM;
+                float mm = kNeutralM;   // the rows' true maximum (with a lazy maximum the reference values lag behind it)
 #pragma unroll
-                for (int w = 0; w < CW; ++w) mm = fmaxf(mm, mw[w]);
+                for (int w = 0; w < CW; ++w) mm = fmaxf(mm, (w < plan.wph) ? src0[w * wstride + D + kMergeTrueMax] : kNeutralM);
                 float ll = 0.f;
                 float4 acc[NV];
 #pragma unroll
@@ -912,7 +1100,10 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
 // compact shape: the register cap (two warps per register-file partition, 5,120 registers each) is
 // what leaves room for the combine launch's CTAs on the same SM
-#define VTEB_COMPACT_BOUNDS __maxnreg__(160)
+#ifndef VTEB_COMPACT_MAXNREG
+#define VTEB_COMPACT_MAXNREG 160
+#endif
+#define VTEB_COMPACT_BOUNDS __maxnreg__(VTEB_COMPACT_MAXNREG)
 
 #define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, BOUNDS)                                                  \
     extern "C" __global__ void BOUNDS NAME(                                                           \

@@ -90,9 +90,17 @@ struct FastPlan {
 
 constexpr int kCtrlBytes = 1024;   // barriers, abort word, tile headers
 constexpr int kStageAlign = 1024;  // stages start on a 1024-byte shared-memory address (the 128-byte swizzle repeats every 8 rows)
-constexpr int kMergePad = 8;       // floats after o[D] in an exchange row: 4 unused, m, l, 2 unused
+constexpr int kMergePad = 8;       // floats after o[D] in an exchange row: 4 unused, m, l, true maximum, 1 unused
 
 __host__ __device__ inline int vteb_round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// 1: 128-wide heads, and 256-wide heads in the full CTA shape, take the transposed form of the block
+// arithmetic (consumer_block.cuh, second half): positions are the M dimension of both products.  A warp
+// then holds all 256 output columns of a head in 64 accumulator registers, so 256-wide heads need no
+// second warp per (head, block).
+#ifndef VTEB_TRANSPOSED
+#define VTEB_TRANSPOSED 1
+#endif
 
 __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_heads, int head_dim, int compact = 0) {
     FastPlan p;
@@ -115,9 +123,9 @@ __host__ __device__ inline FastPlan make_fast_plan(int num_q_heads, int num_kv_h
     if (cap > cw) cap = cw;
     int hg = 1;
     for (int d = 1; d <= cap; ++d) if (num_kv_heads % d == 0) hg = d;
-    // 256-wide heads: two warps share a (head, block), each owning half of the output
-    // columns (both compute the scores); halves the accumulator registers per warp.
-    const int dsplit = (head_dim == 256) ? 2 : 1;
+    // 256-wide heads in the untransposed form: two warps share a (head, block), each owning half of the
+    // output columns (both compute the scores); halves the accumulator registers per warp.
+    const int dsplit = (head_dim == 256 && (compact || !VTEB_TRANSPOSED)) ? 2 : 1;
     p.hg = hg;
     p.n_hgroups = num_kv_heads / hg;
     p.wph = cw / (hg * dsplit);

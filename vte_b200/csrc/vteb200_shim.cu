@@ -664,7 +664,10 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
         if ((rc = check_rt(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g_device), "sm count"))) return rc;
         n_ctas = sms;
     }
-    if (n_ctas > items) n_ctas = (int)items;
+    const bool balanced = (flags & VTEB_ATTN_BALANCED) != 0;
+    if (balanced && max_chunks < 2) return fail(VTEB_ERR_INVALID_ARGUMENT, "VTEB_ATTN_BALANCED needs max_chunks >= 2");
+    if (balanced && compact) return fail(VTEB_ERR_INVALID_ARGUMENT, "VTEB_ATTN_BALANCED and VTEB_ATTN_COMPACT exclude each other");
+    if (n_ctas > items && !balanced) n_ctas = (int)items;
 
     typedef void (*FastKernel)(const __half*, const __half*, const __half*, float*, float*, float*, int, int,
                                int, float, const int*, int, int, int, int, int, const int*, int*, int*, const __half*,
@@ -683,6 +686,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
         g_fast_attr_set[slot] = true;
     }
     int kflags = (flags & VTEB_ATTN_WRITE_EMPTY_O) ? kFlagWriteEmptyO : 0;
+    if (balanced) kflags |= kFlagBalanced;
     // Whole tiles travel as tensor-map boxes when the caches are one matrix of position rows
     // (the stride between sequences is a whole number of rows).
     vteb::KvTensorMap tmk, tmv;
