@@ -279,6 +279,17 @@ def test_direct_entry_point_equals_dispatcher_path(cuda_runtime, codegen):
                 assert np.array_equal(out, out_disp)
             else:
                 assert_parity(out, out_disp)
+        # equal shares of all positions per CTA (VTEB_ATTN_BALANCED): same result, other cuts
+        from vte_b200.bridge.cuda_runtime import ATTN_BALANCED, ATTN_COMPACT
+        rt.split_kv_decode(dq, dk, dv, doff, dout, True, pm, pl, po, work, B, Hq, Hkv, D, cfg.scale,
+                           cfg.kv_batch_stride, C, 0, ATTN_BALANCED)
+        rt.check_status(work)
+        out = np.zeros((B, Hq, D), dtype=np.float32)
+        rt.safe_memcpy_device_to_host(out, dout, "out output")
+        assert_parity(out, out_disp)
+        with pytest.raises(CudaSafetyError):
+            rt.split_kv_decode(dq, dk, dv, doff, dout, True, pm, pl, po, work, B, Hq, Hkv, D, cfg.scale,
+                               cfg.kv_batch_stride, C, 0, ATTN_BALANCED | ATTN_COMPACT)
         with pytest.raises(CudaSafetyError):
             rt.split_kv_decode(dq, dk, dv, doff, dout, True, pm, pl, po, work, B, Hq, Hkv, 96, cfg.scale,
                                cfg.kv_batch_stride, C, 0, 0)
