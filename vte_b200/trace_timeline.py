@@ -1,6 +1,6 @@
 """Timeline of the split and combine kernels inside a replayed decode graph.
 
-    python -m vte_b200.trace_timeline [--workload c2] [--layers 28] [--variant auto] [--define NAME=VALUE ...]
+    python -m vte_b200.trace_timeline [--workload c2] [--layers 28] [--batch N] [--variant auto] [--define NAME=VALUE ...]
 
 Builds the decode-attention cubin with -DVTEB_TRACE=1, which makes lane 0 of every warp of three
 CTAs (first, middle, last but two) stamp the SM cycle counter at fixed points of the split kernel
@@ -42,6 +42,7 @@ def main(argv=None) -> int:
     ap.add_argument("--workload", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--variant", default="auto")
+    ap.add_argument("--batch", type=int, default=0, help="keep only the first N sequences of the workload (0 = all)")
     ap.add_argument("--first", type=int, default=10, help="first launch (layer) to print")
     ap.add_argument("--count", type=int, default=3)
     ap.add_argument("--define", action="append", default=[], help="extra NAME=VALUE macro for the kernel build")
@@ -53,6 +54,10 @@ def main(argv=None) -> int:
 
     cfg = CONFIGS[a.workload]
     lengths = draw_context_lengths(cfg)
+    if a.batch:
+        from dataclasses import replace
+        cfg = replace(cfg, batch=min(a.batch, cfg.batch))
+        lengths = lengths[:cfg.batch]
     L = a.layers
     rt = CudaRuntime(device_index=0)
     rt.initialize()
