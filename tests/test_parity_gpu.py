@@ -174,8 +174,8 @@ def test_ragged_batch_matches_oracle(cuda_runtime, codegen):
 
 
 @pytest.mark.parametrize("shape", [(16, 32, 8, 64, 100, 4096), (5, 12, 2, 128, 1, 3000), (6, 8, 2, 256, 40, 2500),
-                                   (3, 28, 4, 128, 700, 9000), (2, 8, 8, 128, 1, 129)],
-                         ids=["d64x16", "d128x5", "d256x6", "d128g7x3", "d128mha_short"])
+                                   (3, 28, 4, 128, 700, 9000), (2, 8, 8, 128, 1, 129), (6, 12, 2, 128, 1, 5000)],
+                         ids=["d64x16", "d128x5", "d256x6", "d128g7x3", "d128mha_short", "d128skewed"])
 def test_balanced_partition_matches_oracle(cuda_runtime, codegen, shape):
     """Several sequences, no split count given: every CTA takes an equal share of all cached positions
     and a sequence is cut wherever a share ends.  The output, and the partial buffers reduced by the
@@ -184,7 +184,10 @@ def test_balanced_partition_matches_oracle(cuda_runtime, codegen, shape):
     from vte_b200.core.split_kv_attention import balanced_pieces
     B, Hq, Hkv, D, lo, hi = shape
     cfg = DecodeConfig("balanced", 31, B, Hq, Hkv, D, lo, hi, 1)
-    q, k, v, off = make_layer_inputs(cfg, 0)
+    # "skewed": one long sequence among very short ones, so that the shares have to grow
+    # (a pair may not be cut into more pieces than it has splits) and CTAs stay idle
+    lens = [5000, 3, 1, 40, 7, 129] if B == 6 and D == 128 else None
+    q, k, v, off = make_layer_inputs(cfg, 0, lengths=lens)
     ref = orc.decode_attention(q, k, v, off)
     for kw in ({}, {"strict_empty_splits": True}, {"num_splits": 3, "balanced": True}):
         ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), cfg.batch, cfg.max_seq, 1, **kw)

@@ -50,6 +50,9 @@
 // (256-wide heads always take one): 2 = one pair per half-warp.  Measured with 12 query heads on six
 // warps (one pass instead of two): the 32k-context layer 10.13 against 10.40 us, its split kernel alone
 // 9.34 against 9.80 us per launch.
+#ifndef VTEB_TMA_LANES
+#define VTEB_TMA_LANES 1   // 1: full shape, the boxes of a tile are issued by as many lanes at once; 0: by one lane in turn
+#endif
 #ifndef VTEB_MERGE_PAIRS
 #define VTEB_MERGE_PAIRS 2
 #endif
@@ -362,6 +365,12 @@ template <int D, int CW, bool kRope = false>
 __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 {
     constexpr bool kCompact = (CW == kCompactConsumerWarps);
+    // Full shape: the boxes of a tile (one per 128-byte column block) are issued by as many lanes in one
+    // warp instruction; issued by one lane in turn they cost the loader about as long as the tile's share of
+    // the stream lasts (one million positions: 157.5 vs 167.1 us per layer, sixteen 256-wide sequences 172.9
+    // vs 177.7).  The compact shape keeps the one lane: its launches live on how soon the FIRST tile lands,
+    // and six tiles' boxes requested at once delay it (32k context: 10.07 vs 9.85 us per layer).
+    constexpr bool kTmaLanes = (VTEB_TMA_LANES != 0) && !kCompact;
     constexpr int kLoaderWarpK = CW;          // loads K rows, owns the work queue
     constexpr int kLoaderWarpV = CW + 1;      // loads V rows, follows the K loader's headers
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -526,7 +535,14 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                         mbar_arrive(bar);                       // every lane: releases its own stores
                     } else if (use_tensor_maps && nvalid == plan.tile) {
                         // a whole tile: one elected lane issues one box per 128-byte column block
-                        if (lane == 0) {
+                        if constexpr (kTmaLanes) {
+                            // one box per lane: the column blocks of a tile are issued by one warp instruction
+                            if (lane == 0) mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
+                            else mbar_arrive(bar);
+                            if (lane < n_col_blocks)
+                                tma_load_box_2d(dst + lane * plan.blk_bytes, a.tmap_k, g.hgroup * plan.hg * D + lane * 64,
+                                                g.b * rows_per_seq + pos0, bar);
+                        } else if (lane == 0) {
                             mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
                             const int x0 = g.hgroup * plan.hg * D, y = g.b * rows_per_seq + pos0;
                             for (int cb = 0; cb < n_col_blocks; ++cb)
@@ -656,7 +672,13 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
                                                     nullptr, 0, -1, 0, lane);
                     mbar_arrive(bar);
                 } else if (use_tensor_maps && hd.nvalid == plan.tile) {
-                    if (lane == 0) {
+                    if constexpr (kTmaLanes) {
+                        if (lane == 0) mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
+                        else mbar_arrive(bar);
+                        if (lane < n_col_blocks)
+                            tma_load_box_2d(dst + lane * plan.blk_bytes, a.tmap_v, hd.hgroup * plan.hg * D + lane * 64,
+                                            hd.b * rows_per_seq + hd.pos0, bar);
+                    } else if (lane == 0) {
                         mbar_arrive_expect_tx(bar, plan.tile * plan.row_bytes);
                         const int x0 = hd.hgroup * plan.hg * D, y = hd.b * rows_per_seq + hd.pos0;
                         for (int cb = 0; cb < n_col_blocks; ++cb)
