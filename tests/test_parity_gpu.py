@@ -174,8 +174,9 @@ def test_ragged_batch_matches_oracle(cuda_runtime, codegen):
 
 
 @pytest.mark.parametrize("shape", [(16, 32, 8, 64, 100, 4096), (5, 12, 2, 128, 1, 3000), (6, 8, 2, 256, 40, 2500),
-                                   (3, 28, 4, 128, 700, 9000), (2, 8, 8, 128, 1, 129), (6, 12, 2, 128, 1, 5000)],
-                         ids=["d64x16", "d128x5", "d256x6", "d128g7x3", "d128mha_short", "d128skewed"])
+                                   (3, 28, 4, 128, 700, 9000), (2, 8, 8, 128, 1, 129), (6, 12, 2, 128, 1, 5000),
+                                   (200, 8, 8, 64, 1, 300)],
+                         ids=["d64x16", "d128x5", "d256x6", "d128g7x3", "d128mha_short", "d128skewed", "d64x200"])
 def test_balanced_partition_matches_oracle(cuda_runtime, codegen, shape):
     """Several sequences, no split count given: every CTA takes an equal share of all cached positions
     and a sequence is cut wherever a share ends.  The output, and the partial buffers reduced by the
