@@ -343,10 +343,14 @@ def test_append_fused_into_the_split_kernel(cuda_runtime, codegen, shape):
     news = [[(rng.standard_normal((B, Hkv, D), dtype=np.float32).astype(np.float16),
               rng.standard_normal((B, Hkv, D), dtype=np.float32).astype(np.float16)) for _ in range(2)] for _ in steps]
     results = {}
-    for fused in (False, True):
-        for variant in ("full", "compact"):
+    # "balanced": the fused append under the balanced partition (pieces instead of fixed splits); its
+    # outputs are compared with the oracle, its cache contents with the other routes bit for bit
+    for fused, variant in ((False, "full"), (False, "compact"), (True, "full"), (True, "compact"), (True, "balanced")):
+        if True:
+            kw = (dict(num_splits=3, balanced=True, variant="full") if variant == "balanced"
+                  else dict(num_splits=3, min_chunk=0, variant=variant))
             ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), B, cfg.max_seq, 2, with_append=True,
-                                         fuse_append=fused, num_splits=3, min_chunk=0, variant=variant)
+                                         fuse_append=fused, **kw)
             try:
                 for l, (q, k, v, _) in enumerate(layers):
                     ex.upload_layer(l, q, k, v)
@@ -379,6 +383,8 @@ def test_append_fused_into_the_split_kernel(cuda_runtime, codegen, shape):
             assert np.array_equal(ka, kb) and np.array_equal(va, vb)
         for bi in range(B):
             assert np.array_equal(a[1][bi][0], caches[0][0][bi]) and np.array_equal(a[1][bi][1], caches[0][1][bi])
+    for (ka, va), (kb, vb) in zip(results[(False, "full")][1], results[(True, "balanced")][1]):
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
 
 
 def test_fp16_output_variant(cuda_runtime, codegen):
