@@ -1,7 +1,12 @@
-// The arithmetic of one 16-position block of the split kernel's consumer warps:
-// S = Q K^T (mma.sync m16n8k16, K fragments via ldmatrix), online softmax in the log2 domain on
-// the accumulator fragment, O += P V (V fragments via ldmatrix.trans) with P carried as an fp16
-// high part in rows 0..7 of the A operand and an fp16 low part in rows 8..15.
+// The arithmetic of one 16-position block of the split kernel's consumer warps, in two forms.
+//
+// First half of the file, query heads as the M dimension (64-wide heads; 256-wide heads in the
+// compact shape): S = Q K^T (mma.sync m16n8k16, K fragments via ldmatrix), online softmax in the
+// log2 domain on the accumulator fragment, O += P V (V fragments via ldmatrix.trans) with P carried
+// as an fp16 high part in rows 0..7 of the A operand and an fp16 low part in rows 8..15.
+// Second half, positions as the M dimension (128-wide heads; 256-wide heads in the full shape):
+// S^T = K Q^T, movmatrix transposes of the P fragments, O^T += V^T P^T.
+// Both keep a reference maximum per row that moves only when a score exceeds it by VTEB_LAZY_MAX.
 //
 // Replaces the per-position loop of
 // vte/compiler/templates/rdna/flash_attention_split_kv_partial.hip.template:92-113

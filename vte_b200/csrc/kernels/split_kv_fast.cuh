@@ -2,15 +2,19 @@
 //
 // grid (n_ctas, 1, 1) persistent, block 320 = eight consumer warps + two loader
 // warps (256 = six + two in the compact shape), dynamic shared memory from
-// make_fast_plan().  A work item is one split
-// of one sequence for one group of `hg` KV heads; item t maps to
-// (sequence rank t / (n_hgroups * C), head group, split).  CTA i starts with
-// item i and draws the following ones from `*ticket` (gridDim.x + atomicAdd).
+// make_fast_plan().  A work item is a range of positions of one sequence for one group of `hg`
+// KV heads, stored as one split of that (sequence, head group).  Two ways to hand them out:
+//   work queue: item t is (sequence rank t / (n_hgroups * C), head group, split) with equal
+//     splits; CTA i starts with item i and draws the following ones from `*ticket`
+//     (gridDim.x + atomicAdd);
+//   balanced partition (kFlagBalanced, full shape): every CTA takes an equal share of all
+//     cached positions and its items are the pieces of sequences inside it (BalancedShare below).
 //
 // Loader warp K (the first warp after the consumers): for every tile of `tile` positions it
 // waits for a free stage, writes the tile header, and fetches the K rows (row_bytes contiguous
-// bytes covering the group's heads): a whole tile as tensor-map box copies issued by one lane
-// (one box of `tile` rows x 64 halves per 128-byte column block), a ragged tile with 16-byte
+// bytes covering the group's heads): a whole tile as tensor-map box copies (one box of `tile`
+// rows x 64 halves per 128-byte column block; issued by as many lanes at once in the full
+// shape, by one lane in turn in the compact shape), a ragged tile with 16-byte
 // asynchronous copies, one 512-byte piece per warp instruction; both write the
 // 128-byte-swizzled tile layout.  Loader warp V (the next warp) follows the headers and
 // fetches the V rows.  Completion is counted on the stage's "full" mbarrier (transaction
@@ -19,13 +23,15 @@
 // numbers.
 //
 // Consumer warp w: KV head (w % hg) of the group, every wph-th 16-position
-// block.  Per block (consumer_block.cuh): S = Q K^T with mma.sync m16n8k16 (Q rows are the query
-// heads of the KV head, K fragments via ldmatrix), online softmax in the log2
-// domain on the accumulator fragment, P split into an fp16 high and low part
-// (high part in rows 0..7 of the A operand, low part in rows 8..15, so one mma
-// multiplies both), O += P V with V fragments via ldmatrix.trans.  At the end of an item the
-// warps of a KV head exchange (m, l, o) through shared memory and the merged
-// state is stored to partial_m / partial_l / partial_o.
+// block.  Per block (consumer_block.cuh, which has both forms): Q K^T and P V with mma.sync
+// m16n8k16, K fragments via ldmatrix, V fragments via ldmatrix.trans, online softmax in the
+// log2 domain on the accumulator fragment with a reference maximum that moves only when a
+// score exceeds it by VTEB_LAZY_MAX, P split into an fp16 high and low part.  128-wide heads
+// (and 256-wide heads in the full shape) take the transposed form, positions as the M
+// dimension of both products; the others the form with the query heads as M and the two
+// parts of P in rows 0..7 and 8..15 of one A operand.  At the end of an item the
+// warps of a KV head exchange (m, l, o) and the row's true maximum through shared memory and
+// the merged state is stored to partial_m / partial_l / partial_o.
 //
 // Under programmatic dependent launch everything that does not depend on the previous launch runs
 // before griddepcontrol.wait: barrier set-up, the first item's geometry (kv offsets, sequence order),
