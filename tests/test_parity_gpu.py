@@ -346,25 +346,24 @@ def test_append_fused_into_the_split_kernel(cuda_runtime, codegen, shape):
     # "balanced": the fused append under the balanced partition (pieces instead of fixed splits); its
     # outputs are compared with the oracle, its cache contents with the other routes bit for bit
     for fused, variant in ((False, "full"), (False, "compact"), (True, "full"), (True, "compact"), (True, "balanced")):
-        if True:
-            kw = (dict(num_splits=3, balanced=True, variant="full") if variant == "balanced"
-                  else dict(num_splits=3, min_chunk=0, variant=variant))
-            ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), B, cfg.max_seq, 2, with_append=True,
-                                         fuse_append=fused, **kw)
-            try:
-                for l, (q, k, v, _) in enumerate(layers):
-                    ex.upload_layer(l, q, k, v)
-                outs = []
-                for si, base in enumerate(steps):
-                    off = np.array([(base + 7 * b) % 200 for b in range(B)], dtype=np.int32)
-                    for l in range(2):
-                        ex.upload_new_kv(l, *news[si][l])
-                    outs.append(ex.execute_decode_batch(off))
-                rows = [ex.download_cache_rows(0, b, 200) for b in range(B)]
-                results[(fused, variant)] = (outs, rows)
-                assert ex.kernel_launches_per_step == (4 if fused else 6)
-            finally:
-                ex.cleanup()
+        kw = (dict(num_splits=3, balanced=True, variant="full") if variant == "balanced"
+              else dict(num_splits=3, min_chunk=0, variant=variant))
+        ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), B, cfg.max_seq, 2, with_append=True,
+                                     fuse_append=fused, **kw)
+        try:
+            for l, (q, k, v, _) in enumerate(layers):
+                ex.upload_layer(l, q, k, v)
+            outs = []
+            for si, base in enumerate(steps):
+                off = np.array([(base + 7 * b) % 200 for b in range(B)], dtype=np.int32)
+                for l in range(2):
+                    ex.upload_new_kv(l, *news[si][l])
+                outs.append(ex.execute_decode_batch(off))
+            rows = [ex.download_cache_rows(0, b, 200) for b in range(B)]
+            results[(fused, variant)] = (outs, rows)
+            assert ex.kernel_launches_per_step == (4 if fused else 6)
+        finally:
+            ex.cleanup()
     # oracle for the whole sequence of steps
     caches = [(k.copy(), v.copy()) for _, k, v, _ in layers]
     for si, base in enumerate(steps):
