@@ -28,9 +28,17 @@ What each function restates (paths are relative to the reference project):
 * `rope_apply`                   vte/compiler/templates/rdna/rope.hip.template:55-97
                                  (the three rotation types; type 0 and type 2
                                  are pinned through the reference's own numpy
-                                 rotation, type 1 has no Python counterpart in
-                                 the reference and is a restatement of the
-                                 template alone: parity unpinned for type 1)
+                                 rotation; type 1, which has no Python
+                                 counterpart in the reference, is pinned like
+                                 the other two through the reference's
+                                 rope_kernel itself, see below)
+
+Second pin: `oracle/build_ref.py` compiles the reference's own kernel templates
+(append, partial, reduce, unsplit, rope) for CPU threads, and
+`tests/golden/make_refkernel_golden.py` stores their outputs as
+`tests/golden/refkernel_*.npz`; `tests/test_reference_kernels_cpu.py` checks
+`kv_cache_append`, `split_kv_partial`, `split_kv_reduce`, `decode_attention` and
+`rope_step` against them (rotation and append bit for bit).
 * `chunk_size_for_cus`           vte/core/split_kv_attention.py:40-49
 """
 from __future__ import annotations

@@ -103,6 +103,38 @@ def test_config1_matches_reference_vector(cuda_runtime, codegen, compat):
         assert_parity(out, gold, tight=5e-5)
 
 
+@pytest.mark.parametrize("name", ["gqa3_d64_c32", "gqa6_d128_c8"])
+def test_reference_kernel_vectors(cuda_runtime, codegen, name):
+    """tests/golden/refkernel_split_kv.npz holds what the reference's own partial / reduce / unsplit kernels
+    produce (their templates compiled for CPU threads, oracle/build_ref.py).  In the reference's fixed-chunk
+    mode both kernel families here must reproduce its partial buffers split for split (neutral state in the
+    chunks past a sequence), and every route's output must match its reduce and unsplit outputs at fp16
+    resolution."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_refkernel_golden", GOLD / "make_refkernel_golden.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    g = np.load(GOLD / "refkernel_split_kv.npz")
+    q, k, v, k_new, v_new, off, chunk, scale = gen.split_case_inputs(name)
+    orc.kv_cache_append(k_new, v_new, k, v, off)
+    B, max_seq, Hkv, D = k.shape
+    cfg = DecodeConfig("refkernel", 0, B, q.shape[1], Hkv, D, 1, max_seq, 1)
+    rm, rl, ro = g[f"{name}.pm"], g[f"{name}.pl"], g[f"{name}.po"]
+    live = rl > 0
+    for compat in (True, False):
+        out, (pm, pl, po), C = run_layer(cuda_runtime, codegen, cfg, q, k, v, off, fixed_chunk_size=chunk, compat=compat,
+                                         strict_empty_splits=True)
+        assert C == rm.shape[2]
+        assert np.array_equal(pm[~live], rm[~live]) and np.all(pl[~live] == 0) and np.all(po[~live] == 0)
+        assert np.allclose(pm[live], rm[live], atol=1e-3)
+        assert np.allclose(pl[live], rl[live], rtol=2e-3, atol=1e-4)
+        assert np.allclose(po[live], ro[live], rtol=2e-3, atol=2e-3)
+        assert np.max(np.abs(out - g[f"{name}.reduce"].astype(np.float32))) <= 1.5e-3
+        assert np.max(np.abs(out - g[f"{name}.unsplit"].astype(np.float32))) <= 1.5e-3
+    out, _, _ = run_layer(cuda_runtime, codegen, cfg, q, k, v, off)           # the dispatcher's own choice of splits
+    assert np.max(np.abs(out - g[f"{name}.reduce"].astype(np.float32))) <= 1.5e-3
+
+
 def test_fixed_chunk_mode_reproduces_reference_chunking(cuda_runtime, codegen):
     """-DSPLIT_KV_CHUNK_SIZE=32 build: split c covers [32c, 32c+32) as in the reference."""
     cfg = CONFIGS["c1"]

@@ -141,3 +141,39 @@ def test_rotation_kernel_handles_several_tokens_and_any_grid(cuda_runtime, codeg
     finally:
         for p in bufs.values():
             rt.safe_free(p, "rope test")
+
+
+@pytest.mark.parametrize("name", ["neox_d128", "interleaved_d64", "partial_d256"])
+def test_rotation_kernel_equals_the_reference_kernel_vectors(cuda_runtime, codegen, name):
+    """tests/golden/refkernel_rope.npz holds the output of the reference's own rope_kernel (its template
+    compiled for CPU threads, oracle/build_ref.py) for the three rotation types; the kernel here must give
+    the same fp16 bits.  The interleaved type has no other pin: the reference has no Python rotation for it."""
+    import importlib.util
+    from pathlib import Path
+    gold = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_refkernel_golden", gold / "make_refkernel_golden.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    g = np.load(gold / "refkernel_rope.npz")
+    q, k, cos_t, sin_t, off, rope_type, rot = gen.rope_case_inputs(name)
+    B, Hq, D = q.shape
+    Hkv = k.shape[1]
+    rt = cuda_runtime
+    _, fn = codegen.load_kernel_safe(rt, "rope", rt.get_gpu_architecture(), "rope_kernel")
+    bufs = {}
+    try:
+        for nm, arr in (("q", q), ("k", k), ("cos", cos_t), ("sin", sin_t), ("off", off)):
+            bufs[nm] = rt.safe_malloc(arr.nbytes, f"rope test {nm} output")
+            rt.safe_memcpy_host_to_device(bufs[nm], arr, f"rope test {nm} output")
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        args = [vp(bufs["q"].value), vp(bufs["k"].value), vp(bufs["cos"].value), vp(bufs["sin"].value),
+                ci(1), ci(Hq), ci(Hkv), ci(D), vp(bufs["off"].value), ci(rope_type), ci(rot)]
+        rt.launch_kernel(fn, (max(1, (Hq * D + 255) // 256), B, 1), (256, 1, 1), args)     # the reference's grid rule
+        rt.synchronize()
+        q2, k2 = np.empty_like(q), np.empty_like(k)
+        rt.safe_memcpy_device_to_host(q2, bufs["q"], "rope test q output")
+        rt.safe_memcpy_device_to_host(k2, bufs["k"], "rope test k output")
+        assert np.array_equal(q2, g[f"{name}.q"]) and np.array_equal(k2, g[f"{name}.k"])
+    finally:
+        for p_ in bufs.values():
+            rt.safe_free(p_, "rope test")
