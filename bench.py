@@ -60,7 +60,7 @@ MIN_TRIAL_MS = 50.0
 # (workload, compact CTA shape).  A rebuilt kernel has another hash and reports traffic null until it
 # is captured again.
 NCU_TRAFFIC_BYTES: dict[str, dict[tuple[str, bool], int]] = {
-    "193b4c82d63f06d9": {("c2", True): 33622016},      # 33.62 MB read, <= 256 B written back (partials stay in L2): three launches of the 8-layer case
+    "cccf62593499f897": {("c2", True): 33621930},      # 33.62 MB read, <= 256 B written back (partials stay in L2): three launches of the 8-layer case
 }
 
 
@@ -709,8 +709,7 @@ def kernel_durations(rt, ex, n_layers, reps=20):
     on the launching stream: duration = elapsed / (replays * layers), which
     includes the in-graph launch gap between consecutive kernels."""
     disp = ex.dispatcher
-    name = ("flash_attention_split_kv_partial_kernel" if disp.compat else
-            f"vteb_split_kv_partial_{'compact_' if disp.compact else ''}{'rope_' if (disp.fuse_rope or disp.fuse_append) else ''}d{disp.head_dim}_kernel")
+    name = "flash_attention_split_kv_partial_kernel" if disp.compat else disp.split_kernel_name
     out = {}
     kinds = ((0, "split_us"),) if disp.fused_combine else ((0, "split_us"), (1, "combine_us"))
     out["combine_us"] = 0.0

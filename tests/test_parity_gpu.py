@@ -589,6 +589,71 @@ def test_compact_cta_shape_matches(cuda_runtime, codegen, name):
     assert_parity(out, np.load(GOLD / "attn_c2_layer0.npz")["out"], tight=2e-5)
 
 
+def test_column_split_for_short_splits(cuda_runtime, codegen):
+    """A short context spread over many splits (no split longer than two blocks): in the compact kernel for
+    128-wide heads the three warps of a KV head split the output columns instead of the blocks and store
+    their columns without a cross-warp merge.  Outputs and partial buffers against the oracle for every
+    context length 1..120, one captured graph replayed; the dispatcher must pick that kernel for this
+    geometry and the ordinary compact kernel for a long context."""
+    cfg = DecodeConfig("colsplit", 41, 1, 12, 2, 128, 1, 120, 1)
+    q, k, v, _ = make_layer_inputs(cfg, 0, lengths=[120])
+    for splits in (8, 148):
+        ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(cfg), 1, cfg.max_seq, 1, num_splits=splits,
+                                     min_chunk=0, variant="compact", strict_empty_splits=True)
+        try:
+            assert ex.dispatcher.split_kernel_name == "vteb_split_kv_partial_compact_cs_d128_kernel"
+            ex.upload_layer(0, q, k, v)
+            for n in list(range(1, 40)) + [47, 48, 49, 64, 65, 96, 97, 119, 120]:
+                off = np.array([n - 1], dtype=np.int32)
+                out = ex.execute_decode_batch(off)[0]
+                ref = orc.decode_attention(q, k, v, off)
+                assert_parity(out, ref, tight=5e-5)
+                pm, pl, po = ex.read_partials()
+                assert_parity(orc.split_kv_reduce(pm, pl, po), ref, tight=5e-5)
+                rm, rl, ro = orc.split_kv_partial(q, k, v, off, cfg.scale, splits)
+                live = rl > 0
+                assert np.array_equal(pl > 0, live) and np.all(pm[~live] == np.float32(-1e30)) and np.all(po[~live] == 0)
+                assert np.allclose(pm[live], rm[live], atol=1e-3) and np.allclose(pl[live], rl[live], rtol=2e-3, atol=1e-4)
+                assert np.allclose(po[live], ro[live], rtol=2e-3, atol=2e-3)
+        finally:
+            ex.cleanup()
+    # the same kernel through the C ABI (VTEB_ATTN_COMPACT | VTEB_ATTN_SHORT_SPLITS)
+    from vte_b200.bridge.cuda_runtime import ATTN_COMPACT, ATTN_SHORT_SPLITS
+    rt, C, bufs = cuda_runtime, 8, []
+    def dev(arr=None, nbytes=None):
+        n = arr.nbytes if arr is not None else nbytes
+        p_ = rt.safe_malloc(n, "colsplit output")
+        if arr is not None:
+            rt.safe_memcpy_host_to_device(p_, arr, "colsplit output")
+        else:
+            rt.safe_memset(p_, n, "colsplit output")
+        bufs.append(p_)
+        return p_
+    try:
+        off = np.array([99], dtype=np.int32)
+        dq, dk, dv, doff = dev(q), dev(k), dev(v), dev(off)
+        dout, work = dev(nbytes=12 * 128 * 4), dev(nbytes=16)
+        pm, pl, po = dev(nbytes=12 * C * 4), dev(nbytes=12 * C * 4), dev(nbytes=12 * C * 128 * 4)
+        outs = []
+        for flags in (ATTN_COMPACT, ATTN_COMPACT | ATTN_SHORT_SPLITS):
+            rt.split_kv_decode(dq, dk, dv, doff, dout, True, pm, pl, po, work, 1, 12, 2, 128, cfg.scale, cfg.kv_batch_stride, C,
+                               0, flags)
+            rt.check_status(work)
+            out = np.zeros((1, 12, 128), dtype=np.float32)
+            rt.safe_memcpy_device_to_host(out, dout, "colsplit output")
+            assert_parity(out, orc.decode_attention(q, k, v, off), tight=5e-5)
+            outs.append(out)
+    finally:
+        for p_ in bufs:
+            rt.safe_free(p_, "colsplit cleanup")
+    long_cfg = CONFIGS["c2"]
+    ex = DecodeAttentionExecutor(cuda_runtime, codegen, metadata(long_cfg), 1, long_cfg.max_seq, 1)
+    try:
+        assert ex.dispatcher.compact and ex.dispatcher.split_kernel_name == "vteb_split_kv_partial_compact_d128_kernel"
+    finally:
+        ex.cleanup()
+
+
 def test_unsplit_path_stores_the_output_in_one_launch(cuda_runtime, codegen):
     """One split: the split launch normalises and stores the output itself (no combine
     launch); chosen automatically for short configured contexts."""

@@ -49,6 +49,7 @@ ATTN_PROGRAMMATIC = 4
 ATTN_COMPACT = 16
 ATTN_NO_TENSOR_MAPS = 32
 ATTN_BALANCED = 64
+ATTN_SHORT_SPLITS = 128
 
 ERR_DEVICE_STATUS = -6
 

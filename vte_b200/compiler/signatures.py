@@ -42,6 +42,7 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_partial_compact_rope_d256_kernel": _FAST_PARTIAL + _ROPE_TAIL + [P, P],
     "vteb_split_kv_partial_compact_d64_kernel": _FAST_PARTIAL,
     "vteb_split_kv_partial_compact_d128_kernel": _FAST_PARTIAL,
+    "vteb_split_kv_partial_compact_cs_d128_kernel": _FAST_PARTIAL,   # the head's warps split the output columns (short splits)
     "vteb_split_kv_partial_compact_d256_kernel": _FAST_PARTIAL,
     "vteb_split_kv_combine_f16_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_f32_kernel": _FAST_COMBINE,

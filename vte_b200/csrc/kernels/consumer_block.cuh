@@ -353,4 +353,65 @@ __device__ __forceinline__ void softmax_pv_t(ConsumerStateT<MT>& st, const float
     }
 }
 
+// Column-split variant of the transposed form: the warps of a KV head all compute the scores of every
+// block of the item (the same S^T, the same maximum and sum) and each accumulates only its own run of
+// 16-column output tiles [mt0, mt0 + nmt), nmt <= NMT.  No warp holds a partial sum over positions, so
+// nothing has to be merged across warps at the end of an item.
+// The state may have more tiles than NMT (the kernel lends the full-width state); tiles 0..NMT-1 are used.
+template <int NMT, int MT>
+__device__ __forceinline__ void softmax_pv_t_cols(ConsumerStateT<MT>& st, const float (&sraw)[4], uint32_t vaddr, int blk_bytes,
+                                                  int left, float scale2, int g, int mt0, int nmt) {
+    static_assert(NMT <= MT, "state too narrow");
+    uint32_t vf[NMT][4];
+#pragma unroll
+    for (int i = 0; i < NMT; ++i)
+        if (i < nmt) {
+            const int mt = mt0 + i;
+            ldmatrix_x4_trans((vaddr ^ ((mt & 3) << 5)) + (mt >> 2) * blk_bytes, vf[i][0], vf[i][1], vf[i][2], vf[i][3]);
+        }
+    const bool valid[2] = {g < left, g + 8 < left};
+    float s[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] = valid[i >> 1] ? sraw[i] * scale2 : kNeutralM;
+    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#if VTEB_LAZY_MAX > 0
+    st.mt[0] = fmaxf(st.mt[0], mx[0]);
+    st.mt[1] = fmaxf(st.mt[1], mx[1]);
+    const bool move = __any_sync(0xffffffffu, (mx[0] > st.m[0] + (float)VTEB_LAZY_MAX) | (mx[1] > st.m[1] + (float)VTEB_LAZY_MAX));
+#else
+    const bool move = true;
+#endif
+    if (move) {
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float m_up = fmaxf(st.m[h], max_over_g(mx[h]));
+            corr[h] = fast_exp2(st.m[h] - m_up);
+            st.l[h] *= corr[h];
+            st.m[h] = m_up;
+        }
+#pragma unroll
+        for (int i = 0; i < NMT; ++i) { st.o[i][0] *= corr[0]; st.o[i][1] *= corr[1]; st.o[i][2] *= corr[0]; st.o[i][3] *= corr[1]; }
+    }
+    float p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = valid[i >> 1] ? fast_exp2(s[i] - st.m[i & 1]) : 0.f;
+    st.l[0] += p[0] + p[2];
+    st.l[1] += p[1] + p[3];
+    uint32_t bh[2], bl[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const __half2 hi = __floats2half2_rn(p[2 * r], p[2 * r + 1]);
+        const float2 hif = __half22float2(hi);
+        bh[r] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
+        bl[r] = movmatrix_trans(pack_half2(p[2 * r] - hif.x, p[2 * r + 1] - hif.y));
+    }
+#pragma unroll
+    for (int i = 0; i < NMT; ++i)
+        if (i < nmt) mma_full(st.o[i], vf[i][0], vf[i][2], vf[i][1], vf[i][3], bh[0], bh[1]);
+#pragma unroll
+    for (int i = 0; i < NMT; ++i)
+        if (i < nmt) mma_full(st.o[i], vf[i][0], vf[i][2], vf[i][1], vf[i][3], bl[0], bl[1]);
+}
+
 }  // namespace vteb

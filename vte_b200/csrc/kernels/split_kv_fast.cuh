@@ -367,7 +367,7 @@ __device__ __forceinline__ void append_row_to_tile_and_cache(const __half* __res
     }
 }
 
-template <int D, int CW, bool kRope = false>
+template <int D, int CW, bool kRope = false, bool kColSplitKernel = false>
 __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 {
     constexpr bool kCompact = (CW == kCompactConsumerWarps);
@@ -763,6 +763,18 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     ConsumerStateT<D / 16> tt;
     st.reset();
     tt.reset();
+    // Column split (the `..._compact_cs_d128_kernel` instantiation; three warps per KV head, partials wanted):
+    // every warp of a head computes the scores of all the item's blocks and accumulates its own 16-column
+    // tiles only, so the item ends without a cross-warp merge.  The scores are computed three times over,
+    // which pays only while an item is a block or two long (512-position context, 28 layers: 5.59 vs 5.85 us
+    // per layer; 32k context, 14 blocks per head and CTA: 13.3 vs 9.9), so the dispatcher picks this kernel
+    // for contexts whose splits cannot exceed 32 positions.  (A kernel of its own: the mere presence of this
+    // path in the compact kernel changed its register allocation and cost the 32k workload 0.5 us per layer.)
+    // The warps that are alone on their
+    // scheduler (sub 1) take four of the eight tiles, the others two each; the accumulators are the first four tiles of `tt`.
+    const bool colsplit = kColSplitKernel && plan.wph == 3 && !(a.flags & kFlagDirectOutput);
+    const int cs_mt0 = (sub == 0) ? 0 : (sub == 1) ? 2 : 6, cs_nmt = (sub == 1) ? 4 : 2;
+    bool cs_pending = false;              // the head's warps have yet to meet before Q may be rewritten
     int stage = 0;
     uint32_t full_parity = 0, merge_parity = 0;
     bool merge_pending = false;           // previous item's readers may still use the exchange area
@@ -816,12 +828,32 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         if (flags & kTileFirst) {
             st.reset();
             tt.reset();
+            if (cs_pending) {
+                // every consumer warp has left the previous item: its Q fragments may be overwritten
+                if (!mbar_wait_bounded(merge_bar0, merge_parity & 1u, abort_word)) {
+                    raise_abort(abort_word, a.status, kStatusMergeTimeout);
+                    return;
+                }
+                merge_parity ^= 1u;
+                cs_pending = false;
+            }
             if (!first_item) load_q(item_b, item_hgroup);
             first_item = false;
         }
 
         const uint32_t tile_base = smem_u32(stages + (size_t)stage * plan.stage_bytes);
         if (flags & kTileFirst) next_blk = sub;
+        if constexpr (kColSplitKernel) {
+            if (colsplit) {
+                for (int r0 = 0; r0 < nvalid; r0 += kBlockPos) {
+                    float sr[4];
+                    qk_block_t<D>(q_frag, (tile_base + r0 * 128 + k_lane_off) | k_lane_x, blk_bytes, sr);
+                    softmax_pv_t_cols<4>(tt, sr, (tile_base + r0 * 128 + v_lane_off) | v_lane_x, blk_bytes, nvalid - r0, scale2, g,
+                                         cs_mt0, cs_nmt);
+                }
+                next_blk = blk0 + blocks_per_tile;          // nothing left for the loop below
+            }
+        }
         for (; next_blk < blk0 + blocks_per_tile; next_blk += plan.wph) {
             const int r0 = (next_blk - blk0) * kBlockPos;
             if (r0 >= nvalid) break;
@@ -850,6 +882,50 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 
         if (flags & kTileLast) {
             stage = (stage + 1 == nstages) ? 0 : stage + 1;
+            if constexpr (kColSplitKernel) {
+                if (colsplit) {
+                    // every warp holds the finished state of its columns: restate it against the rows' true
+                    // maximum and store it; the warps with sub 0 store m and l
+                    const bool empty = (flags & kTileEmpty) != 0;
+                    const bool write_o = !empty || (a.flags & kFlagWriteEmptyO);
+                    const long long stat_base = ((long long)item_b * a.num_q_heads + (long long)item_hgroup * plan.hg * group +
+                                                 (long long)hh * group) * a.max_chunks + item_c;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int r = 2 * t + h;
+                        float l_head = sum_over_g(tt.l[h]);
+#if VTEB_LAZY_MAX > 0
+                        const float m_head = max_over_g(tt.mt[h]);
+#else
+                        const float m_head = tt.m[h];
+#endif
+                        const float f = fast_exp2(tt.m[h] - m_head);
+                        l_head *= f;
+                        if (r < group) {
+                            const long long stat = stat_base + (long long)r * a.max_chunks;
+                            if (write_o) {
+                                float* orow = a.partial_o + stat * D + g;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    if (i < cs_nmt) {
+                                        orow[(cs_mt0 + i) * 16] = tt.o[i][h] * f;
+                                        orow[(cs_mt0 + i) * 16 + 8] = tt.o[i][2 + h] * f;
+                                    }
+                            }
+                            if (sub == 0 && g == 0) {
+                                a.partial_m[stat] = empty ? kNeutralM : m_head * kLn2;
+                                a.partial_l[stat] = empty ? 0.f : l_head;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(merge_bar0);
+                    cs_pending = true;
+                    VTEB_TR(tr, 6);
+                    VTEB_TR(tr, 7);
+                    continue;
+                }
+            }
             // ---- exchange (m, l, o) between the warps of each KV head and store the item
             const int pitch = D + kMergePad;           // floats per (warp, row): o[D], 4 unused, m, l, true maximum, 1 unused
             if (plan.wph == 1 && !kT) {
@@ -1133,7 +1209,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
 #endif
 #define VTEB_COMPACT_BOUNDS __maxnreg__(VTEB_COMPACT_MAXNREG)
 
-#define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, BOUNDS)                                                  \
+#define VTEB_FAST_PARTIAL_CS(NAME, DIM, CWARPS, BOUNDS, COLSPLIT)                                     \
     extern "C" __global__ void BOUNDS NAME(                                                           \
         const __half* __restrict__ q, const __half* __restrict__ k_cache,                             \
         const __half* __restrict__ v_cache, float* __restrict__ partial_m,                            \
@@ -1158,7 +1234,7 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         a.k_new = nullptr; a.v_new = nullptr;                                                         \
         a.tmap_k = &tmap_k; a.tmap_v = &tmap_v;                                                       \
         (void)head_dim;                                                                               \
-        fast_partial_body<DIM, CWARPS>(a);                                                            \
+        fast_partial_body<DIM, CWARPS, false, COLSPLIT>(a);                                           \
     }
 
 // The same kernel with the Q rotation folded into the Q load: `q` is the un-rotated projection,
@@ -1195,12 +1271,14 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
         fast_partial_body<DIM, CWARPS, true>(a);                                                      \
     }
 
+#define VTEB_FAST_PARTIAL(NAME, DIM, CWARPS, BOUNDS) VTEB_FAST_PARTIAL_CS(NAME, DIM, CWARPS, BOUNDS, false)
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_d64_kernel, 64, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_d128_kernel, 128, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_d256_kernel, 256, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_compact_d64_kernel, 64, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_compact_d128_kernel, 128, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
 VTEB_FAST_PARTIAL(vteb_split_kv_partial_compact_d256_kernel, 256, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS)
+VTEB_FAST_PARTIAL_CS(vteb_split_kv_partial_compact_cs_d128_kernel, 128, kCompactConsumerWarps, VTEB_COMPACT_BOUNDS, true)
 VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d64_kernel, 64, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
 VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d128_kernel, 128, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))
 VTEB_FAST_PARTIAL_ROPE(vteb_split_kv_partial_rope_d256_kernel, 256, kFullConsumerWarps, __launch_bounds__(kFullThreads, 1))

@@ -135,7 +135,7 @@ int check_nccl(int r, const char* what) {
 
 // Per-process record of which in-library kernels already had their dynamic
 // shared memory limit raised.
-bool g_fast_attr_set[6] = {false, false, false, false, false, false};
+bool g_fast_attr_set[7] = {false, false, false, false, false, false, false};
 
 // Tensor map over a K or V cache seen as a matrix of `n_rows` position rows of `row_halves`
 // fp16 values: boxes of 64 halves x `box_rows` rows, 128-byte swizzle.
@@ -675,6 +675,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
     FastKernel fk;
     int slot;
     if (compact && head_dim == 64) { fk = vteb_split_kv_partial_compact_d64_kernel; slot = 3; }
+    else if (compact && head_dim == 128 && (flags & VTEB_ATTN_SHORT_SPLITS) && max_chunks > 1) { fk = vteb_split_kv_partial_compact_cs_d128_kernel; slot = 6; }
     else if (compact && head_dim == 128) { fk = vteb_split_kv_partial_compact_d128_kernel; slot = 4; }
     else if (compact) { fk = vteb_split_kv_partial_compact_d256_kernel; slot = 5; }
     else if (head_dim == 64) { fk = vteb_split_kv_partial_d64_kernel; slot = 0; }
