@@ -187,7 +187,7 @@ int vteb_combine_rows_epl(int rows, int head_dim);
 #define VTEB_ATTN_PROGRAMMATIC 4
 #define VTEB_ATTN_COMPACT 16   /* compact CTA shape where it applies, see vteb_split_kv_plan_compact */
 #define VTEB_ATTN_NO_TENSOR_MAPS 32   /* fetch every tile with 16-byte asynchronous copies (no tensor-map copies) */
-#define VTEB_ATTN_SHORT_SPLITS 128 /* hint: no split is longer than about 32 positions (short contexts spread over many
+#define VTEB_ATTN_SHORT_SPLITS 128 /* hint: no split is longer than 16 positions (short contexts spread over many
                                       splits); the compact kernel for 128-wide heads then lets the warps of a KV head
                                       split the output columns instead of the blocks.  Correct at any length */
 #define VTEB_ATTN_BALANCED 64   /* several sequences: every CTA takes an equal share of all cached positions; a

@@ -268,15 +268,17 @@ class SplitKVAttentionDispatcher:
 
     @property
     def split_kernel_name(self) -> str:
-        """Symbol of the fast split kernel this dispatcher launches.  `compact_cs`: splits of one or two
-        16-position blocks (a short context spread over every SM) in the compact kernel for 128-wide heads
+        """Symbol of the fast split kernel this dispatcher launches.  `compact_cs`: splits of one
+        16-position block (a context of up to 16 positions per SM) in the compact kernel for 128-wide heads
         with three warps per KV head: the head's warps split the output columns instead of the blocks and
-        the item ends without a cross-warp merge (512-position context: 5.59 against 5.85 us per layer;
-        with longer splits the repeated score computation costs more than the merge)."""
+        the item ends without a cross-warp merge.  Measured per layer, 28 layers per graph, column split
+        against the ordinary compact kernel: 512 positions 5.62 / 5.85 us, 1,024: 5.79 / 6.13, 2,048:
+        5.88 / 6.37, 4,096 (two blocks per split): 6.42 / 6.35, 8,192: 7.59 / 7.09, 16,384: 9.67 / 8.34:
+        from two blocks on, the repeated score computation costs more than the merge."""
         rotating = self.fuse_rope or self.fuse_append
         longest_split = -(-self.context_length // max(1, self.max_chunks))
         column_split = (self.compact and not rotating and self.head_dim == 128 and self._plan.hg == 2
-                        and self.max_chunks > 1 and -(-longest_split // 16) * 16 <= 32)
+                        and self.max_chunks > 1 and longest_split <= 16)
         return (f"vteb_split_kv_partial_{'compact_' if self.compact else ''}{'cs_' if column_split else ''}"
                 f"{'rope_' if rotating else ''}d{self.head_dim}_kernel")
 

@@ -766,9 +766,9 @@ __device__ __forceinline__ void fast_partial_body(const FastArgs& a)
     // Column split (the `..._compact_cs_d128_kernel` instantiation; three warps per KV head, partials wanted):
     // every warp of a head computes the scores of all the item's blocks and accumulates its own 16-column
     // tiles only, so the item ends without a cross-warp merge.  The scores are computed three times over,
-    // which pays only while an item is a block or two long (512-position context, 28 layers: 5.59 vs 5.85 us
-    // per layer; 32k context, 14 blocks per head and CTA: 13.3 vs 9.9), so the dispatcher picks this kernel
-    // for contexts whose splits cannot exceed 32 positions.  (A kernel of its own: the mere presence of this
+    // which pays only while an item is one block long (28 layers per graph, us per layer: 512-position
+    // context 5.62 vs 5.85, 2,048: 5.88 vs 6.37, 4,096 = two blocks per item: 6.42 vs 6.35, 32k = 14 blocks:
+    // 13.3 vs 9.9), so the dispatcher picks this kernel for contexts whose splits cannot exceed 16 positions.  (A kernel of its own: the mere presence of this
     // path in the compact kernel changed its register allocation and cost the 32k workload 0.5 us per layer.)
     // The warps that are alone on their
     // scheduler (sub 1) take four of the eight tiles, the others two each; the accumulators are the first four tiles of `tt`.
