@@ -117,10 +117,14 @@ def choose_split_count(num_sms: int, batch: int, n_hgroups: int, context_length:
     """
     if context_length <= UNSPLIT_MAX_CONTEXT:
         return 1                                   # unsplit: the split launch stores the output itself
+    # one sequence: a split per SM, but no more splits than the context has 16-position blocks (a short
+    # context then launches fewer CTAs and its combine reads fewer rows; 512 positions, per layer:
+    # 5.66 / 5.44 / 5.53 / 5.62 us with 16 / 32 / 64 / 148 splits)
+    blocks = max(1, -(-context_length // 16))
     if batch * n_hgroups <= 1:
-        return max(1, min(MAX_SPLITS, num_sms))
+        return max(1, min(MAX_SPLITS, num_sms, blocks))
     if batch == 1:
-        return max(1, min(MAX_SPLITS, num_sms // n_hgroups))
+        return max(1, min(MAX_SPLITS, num_sms // n_hgroups, blocks))
     chunk = choose_chunk_positions(num_sms, batch, n_hgroups, context_length)
     return max(1, min(MAX_SPLITS, math.ceil(context_length / chunk)))
 
@@ -329,7 +333,10 @@ class SplitKVAttentionDispatcher:
                 self._kernel_cache['partial'] = load('decode_attention', self.split_kernel_name)
                 # short split lists (batched decode): one warp per (sequence, head) row;
                 # long ones (one sequence spread over every SM): one CTA per 32 columns
-                self._rows_combine = self.max_chunks <= 64
+                # (the compact split kernel keeps the wide combine at any split count: its CTAs of 76 registers
+                # sit beside a compact split CTA, the row kernel's of 111 do not; 512-position context with 32
+                # splits: 5.44 us per layer with the wide combine, 7.26 with the row kernel)
+                self._rows_combine = self.max_chunks <= 64 and not self.compact
                 self._kernel_cache['reduce'] = load(
                     'decode_attention',
                     'vteb_split_kv_combine_rows_kernel' if self._rows_combine else

@@ -708,7 +708,7 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                    (const vteb::KvTensorMap)tmk, (const vteb::KvTensorMap)tmv);
     if (rc) return rc;
 
-    if (max_chunks <= 64) {
+    if (max_chunks <= 64 && !compact) {       // the wide combine's CTAs fit beside a compact split CTA, the row kernel's do not
         const int rows = batch * num_q_heads;
         const int epl = vteb_combine_rows_epl(rows, head_dim);
         const int units = rows * (head_dim / (32 * epl));
