@@ -48,6 +48,7 @@ KERNEL_SIGNATURES = {
     "vteb_split_kv_combine_f32_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_state_kernel": _FAST_COMBINE,
     "vteb_split_kv_combine_rows_kernel": [P, P, P, P, I, I, I, I, P, I, I],
+    "vteb_split_kv_combine_small_kernel": [P, P, P, P, I, I, I, I, P, I, I],
     "vteb_merge_shard_states_kernel": [P, P, I, I, I],
     "vteb_push_shard_state_kernel": [P, ctypes.Structure, I, I, I, I, I, P],
     "vteb_merge_shard_states_p2p_kernel": [P, P, P, I, I, I, I, I, P, P],

@@ -36,6 +36,7 @@ FLAG_TENSOR_MAPS = 4
 FLAG_PREFETCH_Q = 8
 FLAG_BALANCED = 16
 COMPACT_MAX_CONTEXT = 262144      # one sequence up to this long: the compact CTA shape (launches of tens of microseconds)
+SHORT_CONTEXT_MAX = 2048          # one sequence up to this many positions: at most 32 splits (see choose_split_count)
 UNSPLIT_MAX_CONTEXT = 128         # below this, one CTA per (sequence, head group) finishes before a combine could launch
 
 
@@ -117,14 +118,18 @@ def choose_split_count(num_sms: int, batch: int, n_hgroups: int, context_length:
     """
     if context_length <= UNSPLIT_MAX_CONTEXT:
         return 1                                   # unsplit: the split launch stores the output itself
-    # one sequence: a split per SM, but no more splits than the context has 16-position blocks (a short
-    # context then launches fewer CTAs and its combine reads fewer rows; 512 positions, per layer:
-    # 5.66 / 5.44 / 5.53 / 5.62 us with 16 / 32 / 64 / 148 splits)
+    # One sequence: a split per SM for a long context; up to SHORT_CONTEXT_MAX positions at most 32 splits
+    # (and never more than the context has 16-position blocks), which the compact shape pairs with the
+    # small combine (one L2 round trip for up to 32 splits).  Per layer, 28 layers per graph, 32 splits +
+    # small combine against a split per block or SM + wide combine: 512 positions 4.89 / 5.48 us, 768:
+    # 5.12 / 5.55, 1,024: 5.19 / 5.57, 1,536: 5.54 / 5.82, 2,048: 5.83 / 5.92, 3,000: 6.33 / 6.28,
+    # 4,096: 6.84 / 6.33.
     blocks = max(1, -(-context_length // 16))
+    short = 32 if context_length <= SHORT_CONTEXT_MAX else MAX_SPLITS
     if batch * n_hgroups <= 1:
-        return max(1, min(MAX_SPLITS, num_sms, blocks))
+        return max(1, min(MAX_SPLITS, num_sms, blocks, short))
     if batch == 1:
-        return max(1, min(MAX_SPLITS, num_sms // n_hgroups, blocks))
+        return max(1, min(MAX_SPLITS, num_sms // n_hgroups, blocks, short))
     chunk = choose_chunk_positions(num_sms, batch, n_hgroups, context_length)
     return max(1, min(MAX_SPLITS, math.ceil(context_length / chunk)))
 
@@ -267,6 +272,7 @@ class SplitKVAttentionDispatcher:
 
         self._kernel_cache = {}
         self._rows_combine = False
+        self._small_combine = False
         self._partial_m = self._partial_l = self._partial_o = self._work = None
         self.enabled = not bool(os.environ.get(ENV_DISABLE_SPLITKV)) and allocator is not None
 
@@ -333,12 +339,16 @@ class SplitKVAttentionDispatcher:
                 self._kernel_cache['partial'] = load('decode_attention', self.split_kernel_name)
                 # short split lists (batched decode): one warp per (sequence, head) row;
                 # long ones (one sequence spread over every SM): one CTA per 32 columns
-                # (the compact split kernel keeps the wide combine at any split count: its CTAs of 76 registers
-                # sit beside a compact split CTA, the row kernel's of 111 do not; 512-position context with 32
-                # splits: 5.44 us per layer with the wide combine, 7.26 with the row kernel)
+                # The compact split kernel needs a combine whose CTAs sit beside its own: the wide combine
+                # (76 registers) or, up to 32 splits, the small one (one warp per 32 columns of a head, every
+                # load in flight at once, 64 registers); the row kernel (111 registers) would start only when
+                # the split CTA has left (512-position context with 32 splits, per layer: 7.26 us with the row
+                # kernel, 5.44 with the wide combine).
+                self._small_combine = self.max_chunks <= 32 and self.compact
                 self._rows_combine = self.max_chunks <= 64 and not self.compact
                 self._kernel_cache['reduce'] = load(
                     'decode_attention',
+                    'vteb_split_kv_combine_small_kernel' if self._small_combine else
                     'vteb_split_kv_combine_rows_kernel' if self._rows_combine else
                     'vteb_split_kv_combine_state_kernel' if self.emit_state else
                     'vteb_split_kv_combine_f32_kernel' if self.output_f32 else 'vteb_split_kv_combine_f16_kernel')
@@ -525,6 +535,11 @@ class SplitKVAttentionDispatcher:
         head = [] if self.fuse_append else [append]
         if self.fused_combine or direct:
             return head + [partial]
+        if self._small_combine:
+            rows = batch * Hq
+            units = rows * (D // 32)
+            combine_args = reduce_args + [ci(out_kind), vp(self._work.ptr), ci(rows), ci(1)]
+            return head + [partial, (reduce_fn, combine_args, ((units + 7) // 8, 1, 1), (256, 1, 1), 0)]
         if self._rows_combine:
             rows = batch * Hq
             epl = self.hip.combine_rows_epl(rows, D)

@@ -669,6 +669,69 @@ extern "C" __global__ void __launch_bounds__(256) vteb_split_kv_combine_rows_ker
     else combine_rows_body<8>(partial_m, partial_l, partial_o, output, out_kind, rows, max_chunks, head_dim);
 }
 
+// Combine for one short sequence (compact split kernel; chosen up to 32 splits, correct up to 64): one warp per
+// (query head, 32 output columns), lane = column, no shared memory, no barrier, and every load of the
+// first 32 splits (m, l and the lane's column of every split's partial_o) is issued before the first use:
+// one L2 round trip.  Capped at 80 registers so that its CTAs sit beside a compact split CTA like the wide
+// combine's (the row kernel above needs 111 and starts only when the split CTA has left).  Same argument
+// list as the row kernel (`epl` is 1); grid (ceil(rows * head_dim / 32 / 8), 1, 1), block 256.
+extern "C" __global__ void __maxnreg__(80) vteb_split_kv_combine_small_kernel(
+    const float* __restrict__ partial_m, const float* __restrict__ partial_l,
+    const float* __restrict__ partial_o, void* __restrict__ output,
+    int num_q_heads, int head_dim, int max_chunks, int out_kind, int* __restrict__ ticket, int rows, int epl)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && ticket != nullptr) *ticket = 0;
+    (void)num_q_heads; (void)epl;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int D = head_dim, groups = D / 32;
+    const int unit = blockIdx.x * 8 + warp;
+    const int row = unit / groups, col = (unit - row * groups) * 32 + lane;
+    if (row >= rows) return;
+    const long long base = (long long)row * max_chunks;
+    const float m0 = (lane < max_chunks) ? partial_m[base + lane] : kNeutralM;
+    const float m1 = (lane + 32 < max_chunks) ? partial_m[base + lane + 32] : kNeutralM;
+    const float l0 = (lane < max_chunks) ? partial_l[base + lane] : 0.f;
+    const float l1 = (lane + 32 < max_chunks) ? partial_l[base + lane + 32] : 0.f;
+    const float* op = partial_o + base * D + col;
+    float x[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) x[k] = (k < max_chunks) ? op[(long long)k * D] : 0.f;
+    float M = fmaxf(m0, m1);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float w0 = (m0 <= -1e29f) ? 0.f : __expf(m0 - M);      // an empty split's partial_o may hold anything
+    const float w1 = (m1 <= -1e29f) ? 0.f : __expf(m1 - M);
+    float L = l0 * w0 + l1 * w1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        const float w = __shfl_sync(0xffffffffu, w0, k);
+        if (w != 0.f) acc = fmaf(x[k], w, acc);
+    }
+    if (max_chunks > 32) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) x[k] = (k + 32 < max_chunks) ? op[(long long)(k + 32) * D] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const float w = __shfl_sync(0xffffffffu, w1, k);
+            if (w != 0.f) acc = fmaf(x[k], w, acc);
+        }
+    }
+    if (out_kind == 3) {
+        float* st = reinterpret_cast<float*>(output) + (long long)row * (D + 2);
+        st[col] = acc;
+        if (col == 0) { st[D] = M; st[D + 1] = L; }
+    } else {
+        const float v = acc / fmaxf(L, 1e-20f);
+        if (out_kind == 2) reinterpret_cast<float*>(output)[(long long)row * D + col] = v;
+        else reinterpret_cast<__half*>(output)[(long long)row * D + col] = __float2half(v);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // KV-range sharding across GPUs (one very long sequence): every GPU reduces its
 // own splits to ONE unnormalised state per query head, laid out as

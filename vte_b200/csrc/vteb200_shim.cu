@@ -708,7 +708,14 @@ int vteb_split_kv_decode(const void* q, const void* k_cache, const void* v_cache
                    (const vteb::KvTensorMap)tmk, (const vteb::KvTensorMap)tmv);
     if (rc) return rc;
 
-    if (max_chunks <= 64 && !compact) {       // the wide combine's CTAs fit beside a compact split CTA, the row kernel's do not
+    if (max_chunks <= 32 && compact) {        // beside a compact split CTA: the small combine (64 registers), not the row kernel (111)
+        const int rows = batch * num_q_heads;
+        const int units = rows * (head_dim / 32);
+        return launch_rt(vteb_split_kv_combine_small_kernel, dim3((units + 7) / 8), dim3(256), 0, s, pdl,
+                         (const float*)partial_m, (const float*)partial_l, (const float*)partial_o, output,
+                         num_q_heads, head_dim, max_chunks, out_is_f32 ? 2 : 1, work, rows, 1);
+    }
+    if (max_chunks <= 64 && !compact) {
         const int rows = batch * num_q_heads;
         const int epl = vteb_combine_rows_epl(rows, head_dim);
         const int units = rows * (head_dim / (32 * epl));
